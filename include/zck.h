@@ -1,0 +1,133 @@
+/* C ABI of libzck_b200: the block-scaled FP8 inference hot path of zig-cu-kernels, written for sm_100a (B200).
+ *
+ * The reference project has no C ABI: its replaceable seam is the `run(*inputs, *outputs)` callable that each
+ * PyTorch op hands to `define` (src/zig_cu_kernels/torch/ops.py:267-272), which ends in `cuLaunchKernel` on a Zig
+ * kernel (src/zig_cu_kernels/runtime.py:413-433). Each entry point below replaces one such launch path and takes the
+ * same operands as the reference kernel's parameter list, as raw device pointers, strides in ELEMENTS, a CUDA device
+ * ordinal and a `cudaStream_t`.
+ *
+ * Common contract of every launching entry point:
+ *   - returns ZCK_OK once the work is queued on `stream`; never synchronizes, never reads device memory;
+ *   - allocates no device memory (the caller owns inputs, outputs and workspaces);
+ *   - on failure returns a negative code and leaves a message for `zck_last_error()` (thread local);
+ *   - empty problems (a zero extent) queue nothing and return ZCK_OK;
+ *   - safe to call from several host threads and inside CUDA graph capture, provided `zck_init(device)` ran before
+ *     the capture began (it creates the per-device status word and raises the kernels' shared-memory limits).
+ */
+#ifndef ZCK_H
+#define ZCK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZCK_OK 0
+#define ZCK_ERR_ARGUMENT (-1)    /* shape, stride, alignment or enum out of contract */
+#define ZCK_ERR_CUDA (-2)        /* a CUDA runtime/driver call failed */
+#define ZCK_ERR_UNSUPPORTED (-3) /* not an sm_100 device, or a variant that is not built */
+
+/* element kinds */
+#define ZCK_BF16 0
+#define ZCK_F32 1
+#define ZCK_FP8_E4M3 2
+
+/* activations: src/zig_cu_kernels/fp8_gemm.py:12 (ACTIVATIONS) */
+#define ZCK_ACT_NONE 0
+#define ZCK_ACT_SILU 1
+#define ZCK_ACT_GELU_TANH 2
+#define ZCK_ACT_GELU 3
+
+/* weight kinds of the norm: zig/rms_norm.zig:861-901 */
+#define ZCK_WEIGHT_NONE 0
+#define ZCK_WEIGHT_BF16 1
+#define ZCK_WEIGHT_F32 2
+#define ZCK_WEIGHT_ZERO_CENTERED 4 /* OR-ed onto BF16 or F32: y = n * (1 + w) */
+
+/* One-time, per-device set-up (status word, shared-memory attributes, driver entry points). Idempotent. Every
+ * launching entry point calls it on first use of a device; call it yourself before a CUDA graph capture. */
+int zck_init(int device);
+
+const char* zck_last_error(void);
+const char* zck_version(void);
+
+/* Replaces `launch_rows` -> kernel `fp8_quantize_rows_{bf16,f32}[_e8m0]`
+ * (src/zig_cu_kernels/fp8_gemm.py:682-707, zig/fp8_quantize.zig:44-69).
+ * x: m rows of k values (BF16 or FP32), row stride x_stride elements, base and row stride multiples of 16 bytes.
+ * codes: contiguous (m, k) E4M3, 8-byte aligned. scales: element (row, g) at scales[g * scale_stride + row];
+ * FP32 (4-byte aligned) or E8M0 bytes. k % 128 == 0. Codes and scales are bit-exact to the reference rules. */
+int zck_quantize_fp8_rows(const void* x, int x_kind, uint64_t x_stride, void* codes, void* scales,
+                          uint64_t scale_stride, int scale_is_e8m0, uint32_t m, uint32_t k, int device, void* stream);
+
+/* Replaces `launch_tiles` -> kernel `fp8_quantize_tiles_{bf16,f32}[_e8m0]`
+ * (src/zig_cu_kernels/fp8_gemm.py:710-738, zig/fp8_quantize.zig:74-118).
+ * w: n rows of k values; one scale per 128 x 128 tile at scales[tile_row * scale_stride + tile_col]; rows past n in
+ * the last tile row are neither read nor counted. */
+int zck_quantize_fp8_tiles(const void* w, int w_kind, uint64_t w_stride, void* codes, void* scales,
+                           uint64_t scale_stride, int scale_is_e8m0, uint32_t n, uint32_t k, int device,
+                           void* stream);
+
+/* Replaces `rms_norm.Launch.launch` -> kernels `rms_norm_<x>[_add_<x>]_weight_*_to_<out>_c*`
+ * (src/zig_cu_kernels/rms_norm.py:392-477, zig/rms_norm.zig:239-322, :474-549).
+ * residual == NULL gives the plain norm of x (then residual_out must be NULL). Otherwise h = x + residual rounded
+ * once to x's kind is stored to residual_out and normalized. y_kind: ZCK_BF16, ZCK_F32, or ZCK_FP8_E4M3 with the
+ * one-element FP32 `fp8_scale` (y = e4m3(norm / fp8_scale)). Outputs may alias x or residual exactly.
+ * width % 8 == 0, width <= 32768; every base pointer and row stride a multiple of 16 bytes (8 for FP8 y). */
+int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stride, const void* residual, uint64_t r_stride,
+                           void* residual_out, uint64_t ro_stride, const void* weight, int weight_kind,
+                           const float* fp8_scale, void* y, int y_kind, uint64_t y_stride, uint32_t rows,
+                           uint32_t width, float eps, int device, void* stream);
+
+/* The scalars the reference passes to its GEMM kernels (src/zig_cu_kernels/torch/fp8_gemm.py:226-227, :303-304;
+ * zig/fp8_gemm_sm89.zig:387-413, :507-538). Strides in elements; a scale stride of 0 broadcasts. */
+typedef struct ZckGemmSizes {
+    uint64_t a_stride;        /* row stride of a (bytes == elements for E4M3), multiple of 16 */
+    uint64_t b_stride;        /* row stride of b / of w_gate and w_up, multiple of 16 */
+    uint64_t sa_row, sa_blk;  /* scale_a[(row) * sa_row + kblock * sa_blk] */
+    uint64_t sb_row, sb_blk;  /* scale_b[(col / 128) * sb_row + kblock * sb_blk]; scale_gate for the gated op */
+    uint64_t su_row, su_blk;  /* scale_up, gated op only */
+    uint64_t out_stride;      /* row stride of out (BF16 elements), multiple of 8 */
+    uint64_t residual_stride; /* row stride of residual (BF16 elements); 0 broadcasts one row */
+    uint32_t m, n, k;         /* n: output columns (f for the gated op); n % 8 == 0, k % 128 == 0 */
+    uint32_t e8m0_bits;       /* bit i set: scale i is E8M0 bytes (0: scale_a, 1: scale_b/gate, 2: scale_up) */
+    int32_t activation;       /* ZCK_ACT_* */
+    int32_t splits;           /* K splits chosen by zck_gemm_plan (1 = no workspace) */
+} ZckGemmSizes;
+
+/* Plan query, pure host: fills `sizes->splits` and returns the workspace the launch needs: `part_bytes` of FP32
+ * partial tiles and `counters` 32-bit tile counters that must be ZERO before the first launch (the kernel leaves
+ * them at zero). Replaces `product_launch(...).part_bytes/.counters` (src/zig_cu_kernels/fp8_gemm.py:288-297). */
+int zck_gemm_plan(ZckGemmSizes* sizes, int gated, int device, size_t* part_bytes, uint32_t* counters);
+
+/* Replaces `product_launch("block128", "store", ...)` -> kernel `fp8_gemm_block128_store_*`
+ * (src/zig_cu_kernels/fp8_gemm.py:354-383, zig/fp8_gemm_sm89.zig:387-419).
+ * out = bf16(act(bf16(sum_kb sa*sb*(A_kb B_kb^T) + bias)) + residual); residual may alias out exactly. */
+int zck_fp8_gemm(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out, const void* bias,
+                 const void* residual, void* ws_parts, void* ws_counters, const ZckGemmSizes* sizes, int device,
+                 void* stream);
+
+/* Replaces `product_launch("block128", "gated", ...)` -> kernel `fp8_gemm_block128_gated_*`
+ * (src/zig_cu_kernels/fp8_gemm.py:475-508, zig/fp8_gemm_sm89.zig:507-559).
+ * out = bf16(bf16(act(g)) * v) [+ residual], g = bf16(A w_gate^T + bias_gate), v = bf16(A w_up^T + bias_up). */
+int zck_fp8_gated_gemm(const void* a, const void* w_gate, const void* w_up, const void* scale_a,
+                       const void* scale_gate, const void* scale_up, void* out, const void* bias_gate,
+                       const void* bias_up, const void* residual, void* ws_parts, void* ws_counters,
+                       const ZckGemmSizes* sizes, int device, void* stream);
+
+/* Device-side wait limits never trap: a role whose wait runs out records where it gave up and the block exits.
+ * `zck_poll_status` reads that record from host-mapped memory without synchronizing.
+ * (The reference traps after 1 s instead: zig/mm_sm100.zig:58-64.) */
+typedef struct ZckStatus {
+    uint32_t code;   /* 0 = nothing recorded; else 1 + role that gave up */
+    uint32_t block;  /* blockIdx.x of the first reporter */
+    uint32_t stage;  /* pipeline stage or K block it waited on */
+    uint32_t count;  /* how many reports since the last clear */
+} ZckStatus;
+int zck_poll_status(int device, ZckStatus* out, int clear);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

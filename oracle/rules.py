@@ -1,0 +1,287 @@
+"""CPU oracle of the block-scaled FP8 hot path. TEST INFRASTRUCTURE ONLY.
+
+This module restates, in plain PyTorch on the CPU, the arithmetic rules that the reference project
+(bobcao3/zig-cu-kernels) pins in its own tests for the five hot-path ops. Only the test suite, the smoke check and
+the CPU-baseline leg of the benchmark may import it; the product package never does.
+
+Parity status: pinned. `tests/golden/*.npz` holds outputs of the reference's own Python functions (run from the
+reference tree by `tests/golden/make_golden.py`), and `tests/test_oracle_golden.py` checks every function here
+against them bit for bit.
+
+Each function names the reference lines it follows (paths are relative to the reference project root).
+"""
+
+import math
+
+import torch
+
+FP8 = torch.float8_e4m3fn
+E8M0 = torch.float8_e8m0fnu
+BF16 = torch.bfloat16
+GROUP = 128
+FP8_MAX = 448.0
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# Quantizer rules (bit-exact)
+# --------------------------------------------------------------------------------------------------------------------
+
+def e8m0_byte_of(quotient):
+    """Least byte b with 2^(b-127) >= quotient, clamped to [0, 254]; 127 for a zero quotient; 255 for NaN or inf.
+
+    Integer restatement of zig/fp8.zig:63-70 on the FP32 bit pattern; equal to the frexp form of
+    tests/test_fp8_gemm.py:207-211 and tests/test_rms_norm.py:167-173."""
+    bits = quotient.float().contiguous().view(torch.int32) & 0x7FFFFFFF
+    byte = ((bits.to(torch.int64) + 0x7FFFFF) >> 23).clamp(max=254)
+    byte = torch.where(bits <= 0x00400000, torch.zeros_like(byte), byte)
+    byte = torch.where(bits == 0, torch.full_like(byte, 127), byte)
+    byte = torch.where(bits >= 0x7F800000, torch.full_like(byte, 255), byte)
+    return byte.to(torch.uint8)
+
+
+def e8m0_decode(byte):
+    """FP32 value of an E8M0 byte: 2^-127 for 0, NaN for 255, else 2^(b-127). zig/fp8.zig:87-91,
+    src/zig_cu_kernels/packs.py:95-99."""
+    exponent = byte.to(torch.int32)
+    bits = torch.where(exponent == 0, torch.full_like(exponent, 0x00400000), exponent << 23)
+    bits = torch.where(exponent == 255, torch.full_like(exponent, 0x7FC00000), bits)
+    return bits.view(torch.float32)
+
+
+def scale_of(amax, scale_dtype):
+    """Scale of one scale group from its FP32 `amax` (NaN-propagating maximum of |x|).
+
+    FP32: amax/448 rounded to nearest, 1 where that quotient is 0. E8M0: the byte of `e8m0_byte_of`.
+    tests/test_fp8_gemm.py:202-211; zig/fp8.zig:54-70."""
+    quotient = (amax.double() / FP8_MAX).float()
+    if scale_dtype == torch.float32:
+        return torch.where(quotient == 0, torch.ones_like(quotient), quotient)
+    return e8m0_byte_of(quotient).view(E8M0)
+
+
+def scale_value(scale):
+    """FP32 value of a scale tensor of either dtype."""
+    if scale.dtype == E8M0:
+        return e8m0_decode(scale.view(torch.uint8))
+    return scale.float()
+
+
+def codes_of(x, scale):
+    """E4M3 codes: x/scale rounded to nearest even, saturated to +-448, NaN kept. tests/test_fp8_gemm.py:214-215;
+    zig/fp8.zig:95-114. For an E8M0 scale the kernel multiplies by the exact reciprocal power of two, which gives the
+    same FP32 value as this division whenever the reciprocal is representable."""
+    return (x.float() / scale_value(scale)).clamp(-FP8_MAX, FP8_MAX).to(FP8)
+
+
+def group_amax(groups, dims):
+    """NaN-propagating maximum of |x| over `dims` (torch.amax propagates NaN). zig/fp8.zig:33-52."""
+    return groups.abs().amax(dims)
+
+
+def quantize_rows(x, scale_dtype=torch.float32):
+    """`quantize_fp8_rows`: one scale per row and 128 values. Returns codes of the shape of `x` and scales
+    `(m, k/128)`. src/zig_cu_kernels/torch/fp8_gemm.py:364-408; tests/test_fp8_gemm.py:262-270."""
+    k = x.shape[-1]
+    m = math.prod(x.shape[:-1])
+    groups = x.float().reshape(m, k // GROUP, GROUP)
+    scales = scale_of(group_amax(groups, -1), scale_dtype)
+    codes = codes_of(groups, scales[..., None]).reshape(x.shape)
+    return codes, scales
+
+
+def quantize_tiles(w, scale_dtype=torch.float32):
+    """`quantize_fp8_tiles`: one scale per 128 x 128 tile; rows past `n` in the last tile row do not count.
+    src/zig_cu_kernels/torch/fp8_gemm.py:411-458; tests/test_fp8_gemm.py:271-285; zig/fp8_quantize.zig:97-103."""
+    n, k = w.shape
+    tile_rows = -(-n // GROUP)
+    padded = torch.zeros(tile_rows * GROUP, k, dtype=torch.float32)
+    padded[:n] = w.float()
+    tiles = padded.reshape(tile_rows, GROUP, k // GROUP, GROUP)
+    scales = scale_of(group_amax(tiles, (1, 3)), scale_dtype)
+    codes = codes_of(tiles, scales[:, None, :, None]).reshape(-1, k)[:n]
+    return codes, scales
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# GEMM rules
+# --------------------------------------------------------------------------------------------------------------------
+
+def activation(name, x):
+    """PyTorch's own op on the given dtype. tests/test_fp8_gemm.py:64-70."""
+    if name == "none":
+        return x
+    if name == "silu":
+        return torch.nn.functional.silu(x)
+    if name == "gelu_tanh":
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if name == "gelu":
+        return torch.nn.functional.gelu(x)
+    raise ValueError(name)
+
+
+def block_factor(scale, rows, k, tiles, dtype=torch.float64):
+    """Per-element factor of a block128 operand with `rows` rows of `k` values. tests/test_fp8_gemm.py:127-139."""
+    values = scale_value(scale).to(dtype)
+    groups = k // GROUP
+    if tiles:
+        return values.reshape(-1, groups).repeat_interleave(GROUP, 0)[:rows].repeat_interleave(GROUP, 1)
+    return values.reshape(rows, groups).repeat_interleave(GROUP, 1)
+
+
+def dequantize(codes, scale, tiles, dtype=torch.float64):
+    """tests/test_fp8_gemm.py:142-144 (FP64) and tests/fp8_mm_references.py:22-24."""
+    rows, k = math.prod(codes.shape[:-1]), codes.shape[-1]
+    return codes.reshape(rows, k).to(dtype) * block_factor(scale, rows, k, tiles, dtype)
+
+
+def block_sums(a, scale_a, b, scale_b, dtype=torch.float64):
+    """`A_deq @ B_deq.T`: the exact (FP64) or FP32 dequantise-and-matmul that the tolerance is stated against.
+    tests/test_fp8_gemm.py:196-199, :490-491; tests/fp8_mm_references.py:35-36."""
+    return dequantize(a, scale_a, False, dtype) @ dequantize(b, scale_b, True, dtype).T
+
+
+def store_epilogue(s, bias, act, residual):
+    """BF16 rounding points of `fp8_gemm` on FP32 sums `s`. tests/test_fp8_gemm.py:494-497;
+    zig/fp8_gemm_sm89.zig:1740-1814."""
+    y = (s.float() + (0.0 if bias is None else bias.float())).bfloat16()
+    y = activation(act, y)
+    return y if residual is None else y + residual.reshape(y.shape)
+
+
+def gated_epilogue(s_gate, s_up, bias_gate, bias_up, act, residual):
+    """BF16 rounding points of `fp8_gated_gemm`. tests/test_fp8_gemm.py:500-504; zig/epilogue.zig:28-30."""
+    g = (s_gate.float() + (0.0 if bias_gate is None else bias_gate.float())).bfloat16()
+    v = (s_up.float() + (0.0 if bias_up is None else bias_up.float())).bfloat16()
+    y = activation(act, g) * v
+    return y if residual is None else y + residual.reshape(y.shape)
+
+
+def fp8_gemm(a, b, scale_a, scale_b, bias=None, act="none", residual=None, dtype=torch.float64):
+    """Whole `fp8_gemm` on the CPU: dequantise, matmul in `dtype`, epilogue. BF16 `(*lead, n)`."""
+    lead = a.shape[:-1]
+    s = block_sums(a, scale_a, b, scale_b, dtype).float()
+    out = store_epilogue(s, bias, act, None if residual is None else residual.reshape(s.shape))
+    return out.reshape(*lead, b.shape[0])
+
+
+def fp8_gated_gemm(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate=None, bias_up=None, act="silu",
+                   residual=None, dtype=torch.float64):
+    lead = a.shape[:-1]
+    s_gate = block_sums(a, scale_a, w_gate, scale_gate, dtype).float()
+    s_up = block_sums(a, scale_a, w_up, scale_up, dtype).float()
+    out = gated_epilogue(s_gate, s_up, bias_gate, bias_up, act,
+                         None if residual is None else residual.reshape(s_gate.shape))
+    return out.reshape(*lead, w_gate.shape[0])
+
+
+def error_terms(a, scale_a, b, scale_b, gamma=2.0**-9):
+    """Exact sums and the reference's allowed accumulation error gamma * sum(|A||B|) (subnormal E4M3 codes may count
+    as zero). tests/test_fp8_gemm.py:147-162, :196-199."""
+    a_hp, b_hp = dequantize(a, scale_a, False), dequantize(b, scale_b, True)
+    total = a_hp.abs() @ b_hp.abs().T
+
+    def normal(hp, codes):
+        magnitude = codes.reshape(hp.shape).float().abs()
+        return hp.abs() * ~((magnitude < 2.0**-6) & (magnitude > 0))
+
+    subnormal = total - normal(a_hp, a) @ normal(b_hp, b).T
+    return a_hp @ b_hp.T, gamma * total + subnormal
+
+
+SLOPES = {"none": 1.0, "silu": 1.10, "gelu_tanh": 1.13, "gelu": 1.13}
+U = 2.0**-8
+
+
+def store_bound(s, error, bias, act, residual):
+    """FP64 reference and allowed error of `fp8_gemm`. tests/test_fp8_gemm.py:169-180."""
+    y = s + (0.0 if bias is None else bias.double())
+    allowed = SLOPES[act] * (error + U * y.abs())
+    reference = activation(act, y)
+    if act != "none":
+        allowed = allowed + U * reference.abs()
+    if residual is not None:
+        reference = reference + residual.double().reshape(reference.shape)
+        allowed = allowed + U * reference.abs()
+    return reference, allowed
+
+
+def gated_bound(s_gate, error_gate, s_up, error_up, bias_gate, bias_up, act, residual):
+    """FP64 reference and allowed error of `fp8_gated_gemm`. tests/test_fp8_gemm.py:183-193."""
+    g = s_gate + (0.0 if bias_gate is None else bias_gate.double())
+    v = s_up + (0.0 if bias_up is None else bias_up.double())
+    activated = activation(act, g)
+    error_g, error_v = error_gate + U * g.abs(), error_up + U * v.abs()
+    reference = activated * v
+    allowed = v.abs() * (SLOPES[act] * error_g + U * activated.abs()) + activated.abs() * error_v
+    allowed = allowed + U * reference.abs()
+    if residual is not None:
+        reference = reference + residual.double().reshape(reference.shape)
+        allowed = allowed + U * reference.abs()
+    return reference, allowed
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# RMS norm rules
+# --------------------------------------------------------------------------------------------------------------------
+
+def rms_norm(h, weight, zero_centered=False, eps=1e-6, out_dtype=None):
+    """The PyTorch sequence the norm is bounded against. tests/test_rms_norm.py:140-149 (`norm_pytorch`):
+    no weight: n0; BF16 weight: w * dtype(n0) (LlamaRMSNorm); FP32 weight: w * n0; zero-centered: n0 * (1 + w)."""
+    hf = h.float()
+    n0 = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps)
+    if weight is None:
+        y = n0
+    elif zero_centered:
+        y = n0 * (1 + weight.float())
+    elif weight.dtype == BF16:
+        y = weight * n0.to(h.dtype)
+    else:
+        y = weight * n0
+    return y.to(h.dtype if out_dtype is None else out_dtype)
+
+
+def rms_norm_exact(h, weight, zero_centered=False, eps=1e-6):
+    """FP64 norm with eps rounded to FP32 first. tests/test_rms_norm.py:152-157 (`norm_exact`)."""
+    h = h.double()
+    eps32 = float(torch.tensor(eps, dtype=torch.float32))
+    n = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps32)
+    if weight is None:
+        return n
+    return n * (1 + weight.double()) if zero_centered else n * weight.double()
+
+
+def fused_add_rms_norm(x, residual, weight, eps=1e-6, zero_centered=False, out_dtype=None):
+    """`(y, h)` with `h = x + residual` rounded once to the dtype of `x` (bit-exact) and `y = rms_norm(h)`.
+    src/zig_cu_kernels/torch/rms_norm.py:491-496; tests/test_rms_norm.py:256-262; zig/rms_norm.zig:796-817."""
+    h = x + residual
+    return rms_norm(h, weight, zero_centered, eps, out_dtype), h
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# Tensor-parallel MLP (new work on top of the five ops; the unsharded composition is the oracle)
+# --------------------------------------------------------------------------------------------------------------------
+
+def mlp(tokens, w_gate, w_up, w_down, scale_dtype=torch.float32, dtype=torch.float32):
+    """SwiGLU MLP through the quantizer and GEMM rules: rows-quantize tokens, gated GEMM, rows-quantize, down GEMM."""
+    a, sa = quantize_rows(tokens, scale_dtype)
+    g, sg = quantize_tiles(w_gate, scale_dtype)
+    u, su = quantize_tiles(w_up, scale_dtype)
+    d, sd = quantize_tiles(w_down, scale_dtype)
+    h = fp8_gated_gemm(a, g, u, sa, sg, su, dtype=dtype)
+    hq, sh = quantize_rows(h, scale_dtype)
+    return fp8_gemm(hq, d, sh, sd, dtype=dtype)
+
+
+def mlp_shard(tokens, w_gate, w_up, w_down, rank, world, scale_dtype=torch.float32, dtype=torch.float32):
+    """BF16 partial `(m, hidden)` of one rank: gate/up sharded by output columns, down by K. The shard boundaries are
+    multiples of 128, so the shard's codes and scales equal slices of the unsharded ones."""
+    inter = w_gate.shape[0]
+    assert inter % (world * GROUP) == 0
+    lo, hi = rank * inter // world, (rank + 1) * inter // world
+    a, sa = quantize_rows(tokens, scale_dtype)
+    g, sg = quantize_tiles(w_gate[lo:hi], scale_dtype)
+    u, su = quantize_tiles(w_up[lo:hi], scale_dtype)
+    d, sd = quantize_tiles(w_down[:, lo:hi], scale_dtype)
+    h = fp8_gated_gemm(a, g, u, sa, sg, su, dtype=dtype)
+    hq, sh = quantize_rows(h, scale_dtype)
+    return fp8_gemm(hq, d, sh, sd, dtype=dtype)

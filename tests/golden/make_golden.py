@@ -1,0 +1,232 @@
+"""Generates the golden vectors of tests/golden/ by running the REFERENCE project's own Python code.
+
+Run once, where the reference tree is mounted:
+
+    python tests/golden/make_golden.py /path/to/zig-cu-kernels
+
+The reference's CPU-runnable pieces are used as they are:
+  * `tests/fp8_mm_references.py`, `tests/pack_references.py`, `src/zig_cu_kernels/packs.py` are imported;
+  * the rule functions inside `tests/test_fp8_gemm.py` and `tests/test_rms_norm.py` cannot be imported as modules
+    (those files query the GPU runtime at import), so their `def`s are cut out of the source with `ast` and executed
+    unchanged in a namespace that holds only `torch`, `math` and the constants they name.
+Inputs are generated here from fixed seeds; only the outputs come from the reference. Nothing in this script is
+needed at test time: the tests read the `.npz` files it writes.
+"""
+
+import ast
+import math
+import pathlib
+import sys
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = pathlib.Path(__file__).resolve().parent
+GROUP = 128
+FP8 = torch.float8_e4m3fn
+E8M0 = torch.float8_e8m0fnu
+
+
+def functions_of(path, names, namespace):
+    """Executes the named top-level functions of the Python file `path` in `namespace`, source unchanged."""
+    tree = ast.parse(path.read_text())
+    wanted = [node for node in tree.body if isinstance(node, ast.FunctionDef) and node.name in names]
+    missing = set(names) - {node.name for node in wanted}
+    if missing:
+        raise SystemExit(f"{path} no longer defines {sorted(missing)}")
+    exec(compile(ast.Module(body=wanted, type_ignores=[]), str(path), "exec"), namespace)
+    return namespace
+
+
+def raw(tensor):
+    """Bit-preserving numpy view (npz has no bf16/fp8 dtypes)."""
+    tensor = tensor.contiguous()
+    if tensor.dtype in (FP8, E8M0):
+        return tensor.view(torch.uint8).numpy()
+    if tensor.dtype == torch.bfloat16:
+        return tensor.view(torch.int16).numpy()
+    return tensor.numpy()
+
+
+def f32_from_bits(bits):
+    return float(np.array([bits], dtype=np.uint32).view(np.float32)[0])
+
+
+def edge_group_inputs(generator):
+    """FP32 scale groups whose largest magnitudes sit on the edges of the scale rules: zeros of both signs, quotients
+    that underflow or sit next to 2^-127, powers of two times 448 with both neighbours, the largest finite value, NaN,
+    both infinities and normal data over a wide range."""
+
+    def spread(amax):
+        values = (torch.rand(GROUP, generator=generator) * 2 - 1) * amax
+        values[int(torch.randint(GROUP, (1,), generator=generator))] = amax
+        return values
+
+    groups = [torch.zeros(GROUP), -torch.zeros(GROUP)]
+    for bits in (1, 2, 223, 224, 225, 447, 448, 449, 0x00400000, 0x007FFFFF, 0x00800000):
+        groups.append(spread(f32_from_bits(bits)))
+    for power in (-149, -140, -128, -127, -126, -125, -60, -9, -1, 0, 1, 7, 60, 118, 119):
+        amax = np.ldexp(np.float32(448), power)
+        for value in (amax, np.nextafter(amax, np.float32(np.inf)), np.nextafter(amax, np.float32(0))):
+            groups.append(spread(float(value)))
+    groups += [spread(3.4028234663852886e38), torch.full((GROUP,), 448.0), torch.full((GROUP,), -448.0)]
+    for special in (math.nan, math.inf, -math.inf):
+        values = spread(1.0)
+        values[5] = special
+        groups.append(values)
+    groups += [torch.randn(GROUP, generator=generator) * sigma for sigma in (1e-38, 1e-30, 1e-3, 1.0, 240.0, 1e30)]
+    return torch.stack(groups)
+
+
+def quantizer_vectors(ref, out):
+    generator = torch.Generator().manual_seed(1)
+    cases = edge_group_inputs(generator)
+    rows, groups = 37, 5
+    order = torch.randperm(rows * groups, generator=generator) % cases.shape[0]
+    # make sure that every edge group appears at least once
+    order[: cases.shape[0]] = torch.arange(cases.shape[0])[: rows * groups]
+    wide = cases[order].reshape(rows, groups * GROUP)
+    for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+        x = wide.to(dtype)
+        out[f"rows_x_{tag}"] = raw(x)
+        grouped = x.float().reshape(rows, groups, GROUP)
+        for scale_dtype, stag in ((torch.float32, "f32"), (E8M0, "e8m0")):
+            scales = ref["reference_scale"](grouped.abs().amax(-1), scale_dtype)
+            codes = ref["reference_codes"](grouped, scales[..., None]).reshape(x.shape)
+            out[f"rows_scales_{tag}_{stag}"] = raw(scales)
+            out[f"rows_codes_{tag}_{stag}"] = raw(codes)
+    for n in (136, 200):
+        order = torch.randperm(n * 3, generator=generator) % cases.shape[0]
+        w = cases[order].reshape(n, 3 * GROUP)
+        # tiles need finite data in most tiles to be informative: keep one special tile column only
+        w[:, :GROUP] = torch.randn(n, GROUP, generator=generator) / 64
+        w[100:110, GROUP: 2 * GROUP] = 0
+        for dtype, tag in ((torch.float32, "f32"), (torch.bfloat16, "bf16")):
+            wt = w.to(dtype)
+            tile_rows = -(-n // GROUP)
+            padded = torch.zeros(tile_rows * GROUP, 3 * GROUP)
+            padded[:n] = wt.float()
+            tiles = padded.reshape(tile_rows, GROUP, 3, GROUP)
+            out[f"tiles{n}_w_{tag}"] = raw(wt)
+            for scale_dtype, stag in ((torch.float32, "f32"), (E8M0, "e8m0")):
+                scales = ref["reference_scale"](tiles.abs().amax((1, 3)), scale_dtype)
+                codes = ref["reference_codes"](tiles, scales[:, None, :, None]).reshape(-1, 3 * GROUP)[:n]
+                out[f"tiles{n}_scales_{tag}_{stag}"] = raw(scales)
+                out[f"tiles{n}_codes_{tag}_{stag}"] = raw(codes)
+
+
+def config1_vectors(ref, references, packs, out):
+    """BASELINE config 1: A bf16 (256,1024) ~ N(0,1), B bf16 (512,1024) ~ N(0,1)/32, seed 0, FP32 block scales by the
+    op rule, product through the reference's fp8_mm_references (dequantise in FP64, matmul, BF16 store)."""
+    generator = torch.Generator().manual_seed(0)
+    m, n, k = 256, 512, 1024
+    a_hp = torch.randn(m, k, generator=generator).bfloat16()
+    b_hp = (torch.randn(n, k, generator=generator) / 32).bfloat16()
+    a_groups = a_hp.float().reshape(m, k // GROUP, GROUP)
+    scale_a = ref["reference_scale"](a_groups.abs().amax(-1), torch.float32)
+    a = ref["reference_codes"](a_groups, scale_a[..., None]).reshape(m, k)
+    b_tiles = b_hp.float().reshape(n // GROUP, GROUP, k // GROUP, GROUP)
+    scale_b = ref["reference_scale"](b_tiles.abs().amax((1, 3)), torch.float32)
+    b = ref["reference_codes"](b_tiles, scale_b[:, None, :, None]).reshape(n, k)
+    atoms = packs.scale_atoms(scale_a, 0)
+    a_deq = references.dequantized(a, atoms, "fp8_b128")
+    b_deq = references.dequantized(b, scale_b, "fp8_b128")
+    exact, magnitude = references.product(a_deq, b_deq)
+    # the BF16 inputs are not stored: they are torch.randn of seed 0 as above, and the tests regenerate them
+    out["c1_a"], out["c1_b"] = raw(a), raw(b)
+    out["c1_scale_a"], out["c1_scale_b"] = raw(scale_a), raw(scale_b)
+    out["c1_out_fp64_path"] = raw(references.bf16_store(exact))
+    out["c1_out_fp32_path"] = raw(references.bf16_store(a_deq.float() @ b_deq.float().t()))
+    # the same product through the helper functions of tests/test_fp8_gemm.py
+    s = ref["dequantized"](a, scale_a, "block128") @ ref["dequantized"](b, scale_b, "block128", tiles=True).T
+    assert torch.equal(s, exact)
+
+
+def epilogue_vectors(ref, out):
+    """Exact operands (codes in {-1,0,1}, power-of-two scales) through `store_expected` / `gated_expected`."""
+    generator = torch.Generator().manual_seed(5)
+    m, n, k = 70, 264, 640
+    a = torch.randint(-1, 2, (m, k), generator=generator).float().to(FP8)
+    b = torch.randint(-1, 2, (n, k), generator=generator).float().to(FP8)
+    up = torch.randint(-1, 2, (n, k), generator=generator).float().to(FP8)
+    blocks = torch.arange(k // GROUP)
+    row = torch.randint(-3, 4, (m, 1), generator=generator)
+    tile = torch.randint(-2, 3, (-(-n // GROUP), 1), generator=generator)
+    tile_up = torch.randint(-2, 3, (-(-n // GROUP), 1), generator=generator)
+    scale_a = torch.exp2((row - blocks[None, :]).float())
+    scale_b = torch.exp2((tile - blocks[None, :] % 2).float())
+    scale_up = torch.exp2((tile_up - blocks[None, :] % 2).float())
+    bias = torch.randn(n, generator=generator).bfloat16()
+    bias_up = torch.randn(n, generator=generator).bfloat16()
+    residual = torch.randn(m, n, generator=generator).bfloat16()
+    s = (ref["dequantized"](a, scale_a, "block128") @ ref["dequantized"](b, scale_b, "block128", tiles=True).T).float()
+    s_up = (ref["dequantized"](a, scale_a, "block128") @
+            ref["dequantized"](up, scale_up, "block128", tiles=True).T).float()
+    for name, tensor in (("a", a), ("b", b), ("up", up), ("scale_a", scale_a), ("scale_b", scale_b),
+                         ("scale_up", scale_up), ("bias", bias), ("bias_up", bias_up), ("residual", residual),
+                         ("s", s), ("s_up", s_up)):
+        out[f"ep_{name}"] = raw(tensor)
+    # "none" is the only activation whose CPU and CUDA bits are the same function by construction
+    out["ep_store_none"] = raw(ref["store_expected"](s, bias, "none", residual))
+    out["ep_store_none_plain"] = raw(ref["store_expected"](s, None, "none", None))
+    out["ep_gated_none"] = raw(ref["gated_expected"](s, s_up, bias, bias_up, "none", residual))
+    out["ep_store_silu_cpu"] = raw(ref["store_expected"](s, bias, "silu", residual))
+    out["ep_gated_silu_cpu"] = raw(ref["gated_expected"](s, s_up, None, bias_up, "silu", None))
+
+
+def norm_vectors(ref, out):
+    generator = torch.Generator().manual_seed(0)
+    index = 0
+    for width in (8, 136, 1000, 2048):
+        for rows in (1, 13):
+            x = (torch.randn(rows, width, generator=generator) * 2).bfloat16()
+            other = (torch.randn(rows, width, generator=generator) * 2).bfloat16()
+            if rows > 1:
+                x[rows // 2] = 0
+                other[rows // 2] = 0
+            w_bf16 = (torch.randn(width, generator=generator) * 0.5 + 1).bfloat16()
+            w_f32 = torch.randn(width, generator=generator) * 0.5 + 1
+            h = x + other
+            out[f"norm{index}_x"], out[f"norm{index}_other"] = raw(x), raw(other)
+            out[f"norm{index}_w_bf16"], out[f"norm{index}_w_f32"] = raw(w_bf16), raw(w_f32)
+            out[f"norm{index}_h"] = raw(h)
+            out[f"norm{index}_y_none"] = raw(ref["norm_pytorch"](h, None, False).bfloat16())
+            out[f"norm{index}_y_bf16"] = raw(ref["norm_pytorch"](h, w_bf16, False).bfloat16())
+            out[f"norm{index}_y_f32"] = raw(ref["norm_pytorch"](h, w_f32, False).bfloat16())
+            out[f"norm{index}_y_zc"] = raw(ref["norm_pytorch"](h, w_bf16, True).bfloat16())
+            if width <= 136:
+                out[f"norm{index}_exact_bf16"] = raw(ref["norm_exact"](h, w_bf16, False))
+            index += 1
+    out["norm_cases"] = np.array(index)
+
+
+def main():
+    root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    sys.path[:0] = [str(root / "src"), str(root / "tests")]
+    import fp8_mm_references as references  # noqa: E402  (the reference's own module)
+    from zig_cu_kernels import packs  # noqa: E402  (the reference's own module, torch only)
+
+    functions = {"none": lambda x: x, "silu": F.silu, "gelu_tanh": lambda x: F.gelu(x, approximate="tanh"),
+                 "gelu": F.gelu}
+    gemm_names = {"reference_scale", "reference_codes", "scale_factor", "dequantized", "scaling_of", "store_expected",
+                  "gated_expected"}
+    ref = functions_of(root / "tests" / "test_fp8_gemm.py", gemm_names,
+                       {"torch": torch, "math": math, "FP8": FP8, "E8M0": E8M0, "SCALE_GROUP": GROUP,
+                        "FUNCTIONS": functions})
+    norm = functions_of(root / "tests" / "test_rms_norm.py", {"norm_pytorch", "norm_exact", "fp32"},
+                        {"torch": torch, "np": np, "BF16": torch.bfloat16, "EPS": 1e-6})
+    quant, gemm, norms = {}, {}, {}
+    quantizer_vectors(ref, quant)
+    config1_vectors(ref, references, packs, gemm)
+    epilogue_vectors(ref, gemm)
+    norm_vectors(norm, norms)
+    np.savez_compressed(HERE / "quantizers.npz", **quant)
+    np.savez_compressed(HERE / "gemm.npz", **gemm)
+    np.savez_compressed(HERE / "norm.npz", **norms)
+    for name in ("quantizers", "gemm", "norm"):
+        print(name, (HERE / f"{name}.npz").stat().st_size, "bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,608 @@
+// Block-scaled FP8 GEMM for sm_100a: out = epilogue(sum_kb sa[i,kb] * sb[j/128,kb] * (A_kb B_kb^T)[i,j]).
+//
+// One persistent CTA per SM walks work units (output tile x K split). Per 128-deep K block the tensor core writes
+// a fresh 128 x 256 FP32 product into one of two tensor-memory buffers (tcgen05.mma, kind::f8f6f4, four K=32
+// steps); two epilogue warpgroups drain it with tcgen05.ld and fold it into register accumulators as
+// acc = fma(product, sa * sb, acc) while the tensor core fills the other buffer. FP32 block scales cannot ride the
+// hardware block-scaling path (that path takes E8M0 only), hence the promotion in CUDA cores.
+//
+// Warp roles (384 threads): 0-7 epilogue (warpgroup g owns TMEM columns g*128..g*128+127; warp w reads lanes
+// 32*(w%4)..), 8 TMA producer, 9 MMA issuer and TMEM owner, 10-11 idle. The third warpgroup hands most of its
+// registers to the epilogue warpgroups, which hold 128 accumulators per thread.
+// Shared memory: 4 stages x (A 128x128 + B 256x128 bytes) = 192 KiB in the 128-byte swizzle layout.
+// Gated (SwiGLU) tiles put [gate 0-63 | up 0-63 | gate 64-127 | up 64-127] rows of the weights into the B tile, so
+// a thread owns the gate and up sums of the same 64 output columns.
+#include <cuda.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "sm100_ptx.cuh"
+#include "zck_device.cuh"
+#include "zck_host.h"
+
+namespace zck {
+
+constexpr int kBM = 128, kBN = 256, kBK = 128;
+constexpr int kStages = 4;
+constexpr int kATile = kBM * kBK, kBTile = kBN * kBK, kStageBytes = kATile + kBTile;
+constexpr int kBoxRows = 64;  // rows of one B box
+constexpr int kThreads = 384, kEpilogueThreads = 256;  // three warpgroups: two epilogue, one for the copy and MMA warps
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr uint32_t kTmemColumns = 512;
+constexpr int kBand = 8;  // M tiles that share a band of the tile walk
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kTileFloats = kBM * kBN;
+
+struct GemmParams {
+    const void* scale_a;
+    const void* scale_b;
+    const void* scale_u;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* bias_u;
+    const __nv_bfloat16* residual;
+    __nv_bfloat16* out;
+    float* parts;
+    uint32_t* counters;
+    uint32_t* status;
+    uint64_t wait_ns;
+    uint64_t sa_row, sa_blk, sb_row, sb_blk, su_row, su_blk, out_stride, residual_stride;
+    uint32_t m, n, k, e8m0_bits;
+    int32_t activation;
+    uint32_t m_tiles, n_tiles, kblocks, splits, units;
+};
+
+struct Shared {
+    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], drain;
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+    volatile uint32_t last;
+};
+
+enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2 };
+
+// Bounded wait: gives up after `wait_ns` (or as soon as another role gave up), records who and where, and returns
+// false. Nothing traps; the block then leaves through the common exit.
+__device__ __forceinline__ bool wait_barrier(Shared* sh, uint32_t bar, uint32_t parity, const GemmParams& p, uint32_t role,
+                                             uint32_t where) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = ptx::global_timer();
+    for (uint32_t spin = 1;; ++spin) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0) {
+            if (sh->abort) return false;
+            if (ptx::global_timer() - start > p.wait_ns) {
+                sh->abort = 1;
+                // Plain stores to the host-mapped record: the first reporter wins approximately, which is all a
+                // diagnostic needs, and no atomic has to cross the bus.
+                volatile uint32_t* status = p.status;
+                if (status[0] == 0u) {
+                    status[1] = blockIdx.x;
+                    status[2] = where;
+                    status[0] = 1u + role;
+                }
+                status[3] = status[3] + 1u;
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float load_scale(const void* base, uint64_t index, bool e8m0) {
+    if (e8m0) return e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
+    return static_cast<const float*>(base)[index];
+}
+
+// The activations return what PyTorch's BF16 CUDA kernels return for the same BF16 input: same expressions in FP32,
+// same libdevice functions, default contraction. The result is rounded to BF16 by the caller.
+template <int ACT>
+__device__ __forceinline__ float activate(float x) {
+    if (ACT == ZCK_ACT_SILU) return x / (1.0f + expf(-x));
+    if (ACT == ZCK_ACT_GELU_TANH) {
+        constexpr float kBeta = (float)(1.41421356237309504880 * 1.12837916709551257390 * 0.5);
+        constexpr float kKappa = 0.044715f;
+        float x_cube = x * x * x;
+        float inner = kBeta * (x + kKappa * x_cube);
+        return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    if (ACT == ZCK_ACT_GELU) {
+        constexpr float kAlpha = (float)0.70710678118654752440;
+        return x * 0.5f * (1.0f + erff(x * kAlpha));
+    }
+    return x;
+}
+
+struct TileCoord {
+    uint32_t m0, n0, tile, split, kb0, kb_count;
+};
+
+template <bool GATED>
+__device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t unit) {
+    TileCoord c;
+    c.split = unit % p.splits;
+    c.tile = unit / p.splits;
+    // Tile walk: bands of kBand M tiles; inside a band the M tile varies fastest, so neighbours share the B tile and
+    // the A tiles of a band stay in L2.
+    const uint32_t band_tiles = kBand * p.n_tiles;
+    const uint32_t band = c.tile / band_tiles, within = c.tile % band_tiles;
+    const uint32_t band_rows = min((uint32_t)kBand, p.m_tiles - band * kBand);
+    const uint32_t mt = band * kBand + within % band_rows, nt = within / band_rows;
+    c.m0 = mt * kBM;
+    c.n0 = nt * (GATED ? kBN / 2 : kBN);
+    const uint32_t base = p.kblocks / p.splits, extra = p.kblocks % p.splits;
+    c.kb0 = c.split * base + min(c.split, extra);
+    c.kb_count = base + (c.split < extra ? 1u : 0u);
+    return c;
+}
+
+// Output phase of one thread: 128 accumulators of row `row`. Store tiles: columns col0 .. col0+127. Gated tiles:
+// acc[0..63] are gate sums and acc[64..127] up sums of columns col0 .. col0+63.
+template <bool GATED, int ACT>
+__device__ __forceinline__ void write_row(const GemmParams& p, const float (&acc)[128], uint32_t row, uint32_t col0) {
+    constexpr int kColumns = GATED ? 64 : 128;
+    __nv_bfloat16* out = p.out + (uint64_t)row * p.out_stride;
+    const __nv_bfloat16* residual = p.residual ? p.residual + (uint64_t)row * p.residual_stride : nullptr;
+#pragma unroll
+    for (int j = 0; j < kColumns; j += 8) {
+        const uint32_t col = col0 + j;
+        if (col >= p.n) break;  // n % 8 == 0: an octet is inside or outside as a whole
+        float bias[8], bias_u[8], res[8], y[8];
+        if (p.bias) {
+            uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+            bias[0] = bf16_lo(w.x); bias[1] = bf16_hi(w.x); bias[2] = bf16_lo(w.y); bias[3] = bf16_hi(w.y);
+            bias[4] = bf16_lo(w.z); bias[5] = bf16_hi(w.z); bias[6] = bf16_lo(w.w); bias[7] = bf16_hi(w.w);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) bias[i] = 0.0f;
+        }
+        if (GATED) {
+            if (p.bias_u) {
+                uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias_u + col));
+                bias_u[0] = bf16_lo(w.x); bias_u[1] = bf16_hi(w.x); bias_u[2] = bf16_lo(w.y); bias_u[3] = bf16_hi(w.y);
+                bias_u[4] = bf16_lo(w.z); bias_u[5] = bf16_hi(w.z); bias_u[6] = bf16_lo(w.w); bias_u[7] = bf16_hi(w.w);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) bias_u[i] = 0.0f;
+            }
+        }
+        if (residual) {
+            uint4 w = ld_global_v4(residual + col);
+            res[0] = bf16_lo(w.x); res[1] = bf16_hi(w.x); res[2] = bf16_lo(w.y); res[3] = bf16_hi(w.y);
+            res[4] = bf16_lo(w.z); res[5] = bf16_hi(w.z); res[6] = bf16_lo(w.w); res[7] = bf16_hi(w.w);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float t = bf16_round(__fadd_rn(acc[j + i], bias[i]));
+            float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
+            if constexpr (GATED) {
+                float v = bf16_round(__fadd_rn(acc[64 + j + i], bias_u[i]));
+                u = bf16_round(__fmul_rn(u, v));
+            }
+            y[i] = residual ? __fadd_rn(u, res[i]) : u;
+        }
+        st_global_v4(out + col, make_uint4(bf16x2_of(y[0], y[1]), bf16x2_of(y[2], y[3]), bf16x2_of(y[4], y[5]),
+                                           bf16x2_of(y[6], y[7])));
+    }
+}
+
+template <bool GATED>
+__device__ __forceinline__ void write_row_any(const GemmParams& p, const float (&acc)[128], uint32_t row, uint32_t col0) {
+    switch (p.activation) {
+        case ZCK_ACT_SILU: write_row<GATED, ZCK_ACT_SILU>(p, acc, row, col0); break;
+        case ZCK_ACT_GELU_TANH: write_row<GATED, ZCK_ACT_GELU_TANH>(p, acc, row, col0); break;
+        case ZCK_ACT_GELU: write_row<GATED, ZCK_ACT_GELU>(p, acc, row, col0); break;
+        default: write_row<GATED, ZCK_ACT_NONE>(p, acc, row, col0); break;
+    }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ CUtensorMap map_u, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // The swizzled tiles need 1024-byte alignment; the dynamic shared memory base only promises 16.
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + (size_t)kStages * kStageBytes);
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t tiles_addr = ptx::smem_addr(tiles);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&sh->full[s]), 1);
+            ptx::mbar_init(ptx::smem_addr(&sh->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_addr(&sh->tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), kEpilogueThreads / 32);
+        }
+        ptx::mbar_init(ptx::smem_addr(&sh->drain), 1);
+        sh->abort = 0;
+        sh->last = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == kProducerWarp && lane == 0) {
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+        if (GATED) ptx::prefetch_tensormap(&map_u);
+    }
+    if (warp == kMmaWarp) {
+        ptx::tmem_alloc(ptx::smem_addr(&sh->tmem_base), kTmemColumns);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp >= 8) {
+      ptx::reg_release<48>();
+      if (warp == kProducerWarp) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
+                const TileCoord c = unit_coord<GATED>(p, unit);
+                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->empty[stage]), phase ^ 1u, p, kRoleProducer, stage))) break;
+                    const uint32_t full = ptx::smem_addr(&sh->full[stage]);
+                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const int32_t x = (int32_t)((c.kb0 + i) * kBK);
+                    ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                    ptx::tma_load_2d(base, &map_a, x, (int32_t)c.m0, full);
+#pragma unroll
+                    for (int box = 0; box < kBN / kBoxRows; ++box) {
+                        const CUtensorMap* map = GATED && (box & 1) ? &map_u : &map_b;
+                        const int32_t y = (int32_t)(c.n0 + (GATED ? (box >> 1) : box) * kBoxRows);
+                        ptx::tma_load_2d(base + kATile + box * kBoxRows * kBK, map, x, y, full);
+                    }
+                }
+            }
+            if (!ok) {
+                // Leave only after the copies already in flight have landed (bounded), so that none arrives in
+                // shared memory that no longer belongs to this block.
+                for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
+                    const uint32_t j = it - back, stage = j % kStages, phase = (j / kStages) & 1u;
+                    for (uint32_t spin = 0; spin < 200000u; ++spin)
+                        if (ptx::mbar_try_wait(ptx::smem_addr(&sh->full[stage]), phase)) break;
+                }
+            }
+        }
+        __syncwarp();
+      } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::idesc_e4m3(kBM, kBN);
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
+                const TileCoord c = unit_coord<GATED>(p, unit);
+                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
+                    if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_empty[buf]), use ^ 1u, p, kRoleMma, 16 + buf))) break;
+                    if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->full[stage]), phase, p, kRoleMma, stage))) break;
+                    ptx::tc_fence_after();
+                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const uint64_t desc_a = ptx::smem_desc_sw128(base), desc_b = ptx::smem_desc_sw128(base + kATile);
+                    const uint32_t tmem_d = tmem_base + buf * kBN;
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kBK / 32; ++k4)
+                        ptx::mma_f8(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, k4);
+                    ptx::mma_commit(ptx::smem_addr(&sh->empty[stage]));
+                    ptx::mma_commit(ptx::smem_addr(&sh->tmem_full[buf]));
+                }
+            }
+            if (!ok && it > 0) {
+                // Let the tensor core finish what was issued before the tensor memory goes back (bounded).
+                ptx::mma_commit(ptx::smem_addr(&sh->drain));
+                for (uint32_t spin = 0; spin < 200000u; ++spin)
+                    if (ptx::mbar_try_wait(ptx::smem_addr(&sh->drain), 0)) break;
+            }
+        }
+        __syncwarp();
+      }
+    } else {
+        ptx::reg_take<232>();
+        const uint32_t group = warp / 4, quarter = warp % 4;
+        const uint32_t lane_row = quarter * 32 + lane;
+        const bool sa_e8m0 = p.e8m0_bits & 1u, sb_e8m0 = p.e8m0_bits & 2u, su_e8m0 = p.e8m0_bits & 4u;
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
+            const TileCoord c = unit_coord<GATED>(p, unit);
+            const uint32_t row = c.m0 + lane_row;
+            const bool row_live = row < p.m;
+            const bool warp_live = c.m0 + quarter * 32 < p.m;
+            // Output columns of this thread and the weight scale tile they fall in.
+            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);
+            const uint32_t scale_tile = min(col0 / kGroup, (p.n - 1) / kGroup);
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
+            float sa_next = row_live ? load_scale(p.scale_a, (uint64_t)row * p.sa_row + (uint64_t)c.kb0 * p.sa_blk, sa_e8m0) : 0.0f;
+            for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                const uint32_t kb = c.kb0 + i;
+                const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
+                const float sa = sa_next;
+                if (row_live && i + 1 < c.kb_count)
+                    sa_next = load_scale(p.scale_a, (uint64_t)row * p.sa_row + (uint64_t)(kb + 1) * p.sa_blk, sa_e8m0);
+                const float f0 = __fmul_rn(sa, load_scale(p.scale_b, (uint64_t)scale_tile * p.sb_row + (uint64_t)kb * p.sb_blk, sb_e8m0));
+                const float f1 = GATED ? __fmul_rn(sa, load_scale(p.scale_u, (uint64_t)scale_tile * p.su_row + (uint64_t)kb * p.su_blk, su_e8m0)) : f0;
+                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, kb))) break;
+                ptx::tc_fence_after();
+                if (warp_live) {
+                    const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + group * 128u;
+#pragma unroll
+                    for (int chunk = 0; chunk < 4; ++chunk) {
+                        uint32_t product[32];
+                        ptx::tmem_ld_32x32(taddr + chunk * 32, product);
+                        ptx::tmem_wait_ld();
+                        const float f = chunk < 2 ? f0 : f1;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            acc[chunk * 32 + j] = __fmaf_rn(__uint_as_float(product[j]), f, acc[chunk * 32 + j]);
+                    }
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+            }
+            if (!ok) break;
+            if (p.splits == 1) {
+                if (row_live) write_row_any<GATED>(p, acc, row, col0);
+                continue;
+            }
+            // Split K: every split stores its partial tile; the split that arrives last adds all of them in split
+            // order (so the bits do not depend on who was last), runs the epilogue and re-arms the counter.
+            // Part layout per unit: [group][column quad][row][4 floats], so that a warp stores 512 contiguous bytes.
+            float* part = p.parts + (uint64_t)unit * kTileFloats + ((uint64_t)group * 32 * kBM + lane_row) * 4;
+            if (row_live) {
+#pragma unroll
+                for (int quad = 0; quad < 32; ++quad)
+                    __stcg(reinterpret_cast<float4*>(part + (uint64_t)quad * kBM * 4),
+                           make_float4(acc[4 * quad], acc[4 * quad + 1], acc[4 * quad + 2], acc[4 * quad + 3]));
+            }
+            __threadfence();
+            ptx::named_barrier(1, kEpilogueThreads);
+            if (threadIdx.x == 0) {
+                const uint32_t arrived = atomicAdd(p.counters + c.tile, 1u);
+                sh->last = arrived == p.splits - 1 ? 1u : 0u;
+                if (arrived == p.splits - 1) p.counters[c.tile] = 0;  // every split of this tile has arrived
+            }
+            ptx::named_barrier(1, kEpilogueThreads);
+            const bool last = sh->last != 0;
+            ptx::named_barrier(1, kEpilogueThreads);  // `last` is read before the next unit may overwrite it
+            if (last && row_live) {
+                __threadfence();
+                const float* first = p.parts + (uint64_t)(c.tile * p.splits) * kTileFloats + ((uint64_t)group * 32 * kBM + lane_row) * 4;
+#pragma unroll
+                for (int quad = 0; quad < 32; ++quad) {
+                    float4 sum = __ldcg(reinterpret_cast<const float4*>(first + (uint64_t)quad * kBM * 4));
+                    for (uint32_t s = 1; s < p.splits; ++s) {
+                        float4 v = __ldcg(reinterpret_cast<const float4*>(first + (uint64_t)s * kTileFloats + (uint64_t)quad * kBM * 4));
+                        sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
+                        sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+                    }
+                    acc[4 * quad] = sum.x; acc[4 * quad + 1] = sum.y; acc[4 * quad + 2] = sum.z; acc[4 * quad + 3] = sum.w;
+                }
+                write_row_any<GATED>(p, acc, row, col0);
+            }
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled g_encode = nullptr;
+static std::mutex g_map_lock;
+
+struct MapKey {
+    const void* base;
+    uint64_t rows, k, stride;
+    uint32_t box_rows;
+    int device;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && k == o.k && stride == o.stride && box_rows == o.box_rows && device == o.device;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& key) const {
+        uint64_t h = reinterpret_cast<uint64_t>(key.base) * 0x9E3779B97F4A7C15ull;
+        h ^= key.rows * 0xC2B2AE3D27D4EB4Full + key.k * 0x165667B19E3779F9ull + key.stride * 31 + key.box_rows * 7 + (uint64_t)key.device;
+        return (size_t)(h ^ (h >> 29));
+    }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// Tensor map of a row-major matrix of bytes [rows, k] with `stride` bytes between rows; box = 128 bytes x box_rows,
+// 128-byte swizzle, zero fill outside the matrix (partial tiles need no special path).
+static int tensor_map_of(const void* base, uint64_t rows, uint64_t k, uint64_t stride, uint32_t box_rows, int device,
+                         CUtensorMap* out) {
+    MapKey key{base, rows, k, stride, box_rows, device};
+    std::lock_guard<std::mutex> lock(g_map_lock);
+    auto found = g_maps.find(key);
+    if (found != g_maps.end()) {
+        *out = found->second;
+        return ZCK_OK;
+    }
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {rows > 1 ? stride : k};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult result = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS)
+        return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (base %p, rows %llu, k %llu, stride %llu)", (int)result,
+                    base, (unsigned long long)rows, (unsigned long long)k, (unsigned long long)stride);
+    if (g_maps.size() >= 8192) g_maps.clear();
+    g_maps.emplace(key, *out);
+    return ZCK_OK;
+}
+
+int init_gemm(int device) {
+    (void)device;
+    if (!g_encode) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        cudaError_t error = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query);
+        if (error != cudaSuccess || query != cudaDriverEntryPointSuccess || !entry)
+            return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        g_encode = reinterpret_cast<EncodeTiled>(entry);
+    }
+    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    return ZCK_OK;
+}
+
+static uint64_t wait_limit_ns() {
+    static uint64_t limit = [] {
+        const char* text = getenv("ZCK_WAIT_LIMIT_NS");
+        uint64_t value = text ? strtoull(text, nullptr, 10) : 0;
+        return value ? value : 2000000000ull;
+    }();
+    return limit;
+}
+
+static void tile_counts(const ZckGemmSizes& s, bool gated, uint32_t* m_tiles, uint32_t* n_tiles) {
+    const uint32_t columns = gated ? kBN / 2 : kBN;
+    *m_tiles = (s.m + kBM - 1) / kBM;
+    *n_tiles = (s.n + columns - 1) / columns;
+}
+
+// K splits: none while the tiles fill at least half of the SMs; otherwise as many as the SMs hold, each at least
+// 4 K blocks deep. A forced count comes from ZCK_FORCE_SPLITS (tests).
+static uint32_t choose_splits(uint32_t tiles, uint32_t kblocks, int sm_count) {
+    static int forced = [] {
+        const char* text = getenv("ZCK_FORCE_SPLITS");
+        return text ? atoi(text) : 0;
+    }();
+    if (forced > 0) return min((uint32_t)forced, kblocks);
+    if (tiles * 2 >= (uint32_t)sm_count) return 1;
+    uint32_t by_sms = (uint32_t)sm_count / tiles, by_depth = kblocks / 4;
+    uint32_t splits = min(by_sms, by_depth);
+    return splits < 1 ? 1 : splits;
+}
+
+static int check_sizes(const ZckGemmSizes* s) {
+    ZCK_REQUIRE(s != nullptr, "sizes is NULL");
+    ZCK_REQUIRE(s->k > 0 && s->k % kBK == 0, "block128 scaling needs a positive k %% 128 == 0, got %u", s->k);
+    ZCK_REQUIRE(s->n % 8 == 0, "the weights need a row count that is a multiple of 8, got %u", s->n);
+    ZCK_REQUIRE(s->activation >= ZCK_ACT_NONE && s->activation <= ZCK_ACT_GELU, "unknown activation %d", s->activation);
+    ZCK_REQUIRE(s->k <= 0x7FFFFF80u && s->m <= 0x7FFFFF00u && s->n <= 0x7FFFFF00u, "m, n or k is too large");
+    return ZCK_OK;
+}
+
+static int launch_gemm(bool gated, const void* a, const void* b, const void* u, const void* scale_a, const void* scale_b,
+                       const void* scale_u, void* out, const void* bias, const void* bias_u, const void* residual,
+                       void* ws_parts, void* ws_counters, const ZckGemmSizes* s, int device, void* stream) {
+    int code = check_sizes(s);
+    if (code != ZCK_OK) return code;
+    if (s->m == 0 || s->n == 0) return ZCK_OK;
+    ZCK_REQUIRE(a && b && scale_a && scale_b && out && (!gated || (u && scale_u)), "an operand pointer is NULL");
+    ZCK_REQUIRE(aligned(a, 16) && aligned(b, 16) && (!gated || aligned(u, 16)), "a and the weights must start at a multiple of 16 bytes");
+    ZCK_REQUIRE((s->m <= 1 || s->a_stride % 16 == 0) && (s->n <= 1 || s->b_stride % 16 == 0),
+                "the row strides of a and the weights must be multiples of 16 bytes");
+    ZCK_REQUIRE((s->m <= 1 || s->a_stride >= s->k) && (s->n <= 1 || s->b_stride >= s->k), "a row stride is below k");
+    ZCK_REQUIRE(aligned(out, 16) && (s->m <= 1 || s->out_stride % 8 == 0), "out needs 16-byte aligned rows");
+    ZCK_REQUIRE(!residual || (aligned(residual, 16) && s->residual_stride % 8 == 0), "residual needs 16-byte aligned rows");
+    ZCK_REQUIRE(!bias || aligned(bias, 16), "bias must start at a multiple of 16 bytes");
+    ZCK_REQUIRE(!bias_u || aligned(bias_u, 16), "bias_up must start at a multiple of 16 bytes");
+    ZCK_REQUIRE((s->e8m0_bits & 1u) || aligned(scale_a, 4), "FP32 scale_a must be 4-byte aligned");
+    ZCK_REQUIRE((s->e8m0_bits & 2u) || aligned(scale_b, 4), "FP32 weight scales must be 4-byte aligned");
+    ZCK_REQUIRE(!gated || (s->e8m0_bits & 4u) || aligned(scale_u, 4), "FP32 scale_up must be 4-byte aligned");
+    DeviceState* state = device_state(device);
+    if (!state) return ZCK_ERR_CUDA;
+    DeviceGuard guard(device);
+    ZCK_CUDA(guard.error);
+
+    GemmParams p;
+    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_u = scale_u;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.bias_u = static_cast<const __nv_bfloat16*>(bias_u);
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.parts = static_cast<float*>(ws_parts);
+    p.counters = static_cast<uint32_t*>(ws_counters);
+    p.status = state->status_device;
+    p.wait_ns = wait_limit_ns();
+    p.sa_row = s->sa_row; p.sa_blk = s->sa_blk; p.sb_row = s->sb_row; p.sb_blk = s->sb_blk;
+    p.su_row = s->su_row; p.su_blk = s->su_blk; p.out_stride = s->out_stride; p.residual_stride = s->residual_stride;
+    p.m = s->m; p.n = s->n; p.k = s->k; p.e8m0_bits = s->e8m0_bits; p.activation = s->activation;
+    tile_counts(*s, gated, &p.m_tiles, &p.n_tiles);
+    p.kblocks = s->k / kBK;
+    p.splits = s->splits < 1 ? 1u : min((uint32_t)s->splits, p.kblocks);
+    uint64_t units = (uint64_t)p.m_tiles * p.n_tiles * p.splits;
+    ZCK_REQUIRE(units <= 0x7FFFFFFFull, "too many work units");
+    p.units = (uint32_t)units;
+    ZCK_REQUIRE(p.splits == 1 || (ws_parts && ws_counters && aligned(ws_parts, 16) && aligned(ws_counters, 4)),
+                "a split-K launch needs the workspace of zck_gemm_plan");
+
+    CUtensorMap map_a, map_b, map_u;
+    if ((code = tensor_map_of(a, s->m, s->k, s->a_stride, kBM, device, &map_a)) != ZCK_OK) return code;
+    if ((code = tensor_map_of(b, s->n, s->k, s->b_stride, kBoxRows, device, &map_b)) != ZCK_OK) return code;
+    map_u = map_b;
+    if (gated && (code = tensor_map_of(u, s->n, s->k, s->b_stride, kBoxRows, device, &map_u)) != ZCK_OK) return code;
+
+    dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (gated) fp8_gemm_kernel<true><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
+    else fp8_gemm_kernel<false><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
+    ZCK_CUDA(cudaGetLastError());
+    return ZCK_OK;
+}
+
+}  // namespace zck
+
+using namespace zck;
+
+extern "C" int zck_gemm_plan(ZckGemmSizes* sizes, int gated, int device, size_t* part_bytes, uint32_t* counters) {
+    int code = check_sizes(sizes);
+    if (code != ZCK_OK) return code;
+    ZCK_REQUIRE(part_bytes && counters, "part_bytes and counters must not be NULL");
+    *part_bytes = 0;
+    *counters = 0;
+    sizes->splits = 1;
+    if (sizes->m == 0 || sizes->n == 0) return ZCK_OK;
+    DeviceState* state = device_state(device);
+    if (!state) return ZCK_ERR_CUDA;
+    uint32_t m_tiles, n_tiles;
+    tile_counts(*sizes, gated != 0, &m_tiles, &n_tiles);
+    uint64_t tiles = (uint64_t)m_tiles * n_tiles;
+    ZCK_REQUIRE(tiles <= 0x7FFFFFFFull, "too many tiles");
+    uint32_t splits = choose_splits((uint32_t)tiles, sizes->k / kBK, state->sm_count);
+    sizes->splits = (int32_t)splits;
+    if (splits > 1) {
+        *part_bytes = (size_t)tiles * splits * kTileFloats * sizeof(float);
+        *counters = (uint32_t)tiles;
+    }
+    return ZCK_OK;
+}
+
+extern "C" int zck_fp8_gemm(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out,
+                            const void* bias, const void* residual, void* ws_parts, void* ws_counters,
+                            const ZckGemmSizes* sizes, int device, void* stream) {
+    return launch_gemm(false, a, b, nullptr, scale_a, scale_b, nullptr, out, bias, nullptr, residual, ws_parts, ws_counters,
+                       sizes, device, stream);
+}
+
+extern "C" int zck_fp8_gated_gemm(const void* a, const void* w_gate, const void* w_up, const void* scale_a,
+                                  const void* scale_gate, const void* scale_up, void* out, const void* bias_gate,
+                                  const void* bias_up, const void* residual, void* ws_parts, void* ws_counters,
+                                  const ZckGemmSizes* sizes, int device, void* stream) {
+    return launch_gemm(true, a, w_gate, w_up, scale_a, scale_gate, scale_up, out, bias_gate, bias_up, residual, ws_parts,
+                       ws_counters, sizes, device, stream);
+}

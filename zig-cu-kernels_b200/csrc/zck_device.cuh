@@ -1,0 +1,112 @@
+// Device helpers shared by the kernels of libzck_b200 (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace zck {
+
+constexpr int kGroup = 128;  // values that share one block scale
+
+// ---------------------------------------------------------------------------------------------------------------
+// Scalar rules of the quantizers. Every FP32 operation names its rounding so that nothing is contracted or flushed.
+// ---------------------------------------------------------------------------------------------------------------
+
+// max that returns NaN when either operand is NaN (fmaxf would drop it); torch.amax propagates NaN the same way.
+__device__ __forceinline__ float max_nan(float a, float b) {
+    float d;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
+__device__ __forceinline__ float abs_f32(float a) { return __uint_as_float(__float_as_uint(a) & 0x7FFFFFFFu); }
+
+template <int LANES>
+__device__ __forceinline__ float max_nan_over_lanes(float v) {
+#pragma unroll
+    for (int mask = LANES / 2; mask > 0; mask >>= 1) v = max_nan(v, __shfl_xor_sync(0xFFFFFFFFu, v, mask));
+    return v;
+}
+
+// FP32 scale of a group: amax / 448 rounded to nearest even; 1 when the quotient is 0 (zero amax or underflow).
+__device__ __forceinline__ float scale_f32_of(float amax) {
+    float q = __fdiv_rn(amax, 448.0f);
+    return q == 0.0f ? 1.0f : q;
+}
+
+// E8M0 byte of a group: least b with 2^(b-127) >= amax/448, clamped to [0,254]; 127 for 0; 255 for inf or NaN.
+__device__ __forceinline__ uint32_t scale_e8m0_of(float amax) {
+    uint32_t mag = __float_as_uint(__fdiv_rn(amax, 448.0f)) & 0x7FFFFFFFu;
+    uint32_t up = min((mag + 0x7FFFFFu) >> 23, 254u);
+    uint32_t byte = mag <= 0x00400000u ? 0u : up;
+    byte = mag == 0u ? 127u : byte;
+    byte = mag >= 0x7F800000u ? 255u : byte;
+    return byte;
+}
+
+// FP32 value of an E8M0 byte: 2^-127 for 0 (a subnormal), NaN for 255.
+__device__ __forceinline__ float e8m0_to_f32(uint32_t byte) {
+    uint32_t bits = byte == 0u ? 0x00400000u : byte << 23;
+    bits = byte == 255u ? 0x7FFFFFFFu : bits;
+    return __uint_as_float(bits);
+}
+
+// Exact reciprocal of an E8M0 scale as FP32: 2^(127-b); NaN for b == 255.
+__device__ __forceinline__ float e8m0_reciprocal(uint32_t byte) {
+    return e8m0_to_f32(byte == 255u ? 255u : 254u - byte);
+}
+
+// Two FP32 values to two E4M3 bytes: round to nearest even, magnitudes above 448 clamp to 448, NaN gives 0x7F.
+// `lo` lands in bits 0-7 and `hi` in bits 8-15.
+__device__ __forceinline__ uint32_t e4m3x2_of(float lo, float hi) {
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t e4m3x4_of(float v0, float v1, float v2, float v3) {
+    return e4m3x2_of(v0, v1) | (e4m3x2_of(v2, v3) << 16);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// BF16 helpers. A BF16 pair sits in one 32-bit word, first element in the low half.
+// ---------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// Round to nearest even, NaN kept as a quiet NaN (same bits as __float2bfloat16_rn).
+__device__ __forceinline__ uint32_t bf16_bits_of(float v) {
+    return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+__device__ __forceinline__ float bf16_round(float v) { return __uint_as_float(bf16_bits_of(v) << 16); }
+__device__ __forceinline__ uint32_t bf16x2_of(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Memory
+// ---------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint4 ld_global_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// Streaming variants: data that is read or written once should not displace what the GEMMs keep in L2.
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void st_global_v2(void* p, uint2 v) {
+    asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+
+}  // namespace zck

@@ -1,0 +1,87 @@
+// Per-device set-up, error text and the status word of libzck_b200.
+#include "zck_host.h"
+
+#include <mutex>
+#include <string.h>
+
+namespace zck {
+
+static thread_local char g_error[512] = "";
+static DeviceState g_devices[kMaxDevices];
+static std::mutex g_init_lock;
+
+int fail(int code, const char* format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(g_error, sizeof(g_error), format, args);
+    va_end(args);
+    return code;
+}
+
+DeviceState* device_state(int device) {
+    if (device < 0 || device >= kMaxDevices) {
+        fail(ZCK_ERR_ARGUMENT, "device %d is out of range", device);
+        return nullptr;
+    }
+    DeviceState* state = &g_devices[device];
+    if (state->ready) return state;
+    return zck_init(device) == ZCK_OK ? state : nullptr;
+}
+
+}  // namespace zck
+
+using namespace zck;
+
+extern "C" const char* zck_last_error(void) { return g_error; }
+
+extern "C" const char* zck_version(void) { return "zck_b200 0.1 (sm_100a)"; }
+
+extern "C" int zck_init(int device) {
+    if (device < 0 || device >= kMaxDevices) return fail(ZCK_ERR_ARGUMENT, "device %d is out of range", device);
+    std::lock_guard<std::mutex> lock(g_init_lock);
+    DeviceState* state = &g_devices[device];
+    if (state->ready) return ZCK_OK;
+    int count = 0;
+    ZCK_CUDA(cudaGetDeviceCount(&count));
+    if (device >= count) return fail(ZCK_ERR_ARGUMENT, "device %d does not exist (%d devices)", device, count);
+    DeviceGuard guard(device);
+    ZCK_CUDA(guard.error);
+    cudaDeviceProp properties;
+    ZCK_CUDA(cudaGetDeviceProperties(&properties, device));
+    if (properties.major != 10)
+        return fail(ZCK_ERR_UNSUPPORTED, "device %d is compute capability %d.%d; this library is built for sm_100a only",
+                    device, properties.major, properties.minor);
+    state->sm_count = properties.multiProcessorCount;
+    state->cc_major = properties.major;
+    void* host = nullptr;
+    ZCK_CUDA(cudaHostAlloc(&host, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+    memset(host, 0, 64);
+    void* mapped = nullptr;
+    ZCK_CUDA(cudaHostGetDevicePointer(&mapped, host, 0));
+    state->status_host = static_cast<uint32_t*>(host);
+    state->status_device = static_cast<uint32_t*>(mapped);
+    int code = init_gemm(device);
+    if (code != ZCK_OK) return code;
+    state->ready = true;
+    return ZCK_OK;
+}
+
+extern "C" int zck_poll_status(int device, ZckStatus* out, int clear) {
+    if (out == nullptr) return fail(ZCK_ERR_ARGUMENT, "out is NULL");
+    if (device < 0 || device >= kMaxDevices) return fail(ZCK_ERR_ARGUMENT, "device %d is out of range", device);
+    DeviceState* state = &g_devices[device];
+    memset(out, 0, sizeof(*out));
+    if (!state->ready) return ZCK_OK;
+    volatile uint32_t* words = state->status_host;
+    out->code = words[0];
+    out->block = words[1];
+    out->stage = words[2];
+    out->count = words[3];
+    if (clear) {
+        words[0] = 0;
+        words[1] = 0;
+        words[2] = 0;
+        words[3] = 0;
+    }
+    return ZCK_OK;
+}

@@ -1,0 +1,62 @@
+// Host-side plumbing shared by the translation units of libzck_b200: thread-local error text, per-device set-up,
+// argument checks. No device memory is ever allocated here (cudaHostAlloc of one page per device is the only
+// allocation, made by zck_init).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/zck.h"
+
+namespace zck {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    int cc_major = 0;
+    uint32_t* status_host = nullptr;    // pinned, mapped: {code, block, stage, count}
+    uint32_t* status_device = nullptr;  // device alias of status_host
+};
+
+int fail(int code, const char* format, ...);
+DeviceState* device_state(int device);  // runs zck_init on first use; nullptr on failure (error text set)
+
+// RAII switch to `device` for the duration of a launch; restores the caller's current device.
+struct DeviceGuard {
+    int previous = -1;
+    bool switched = false;
+    cudaError_t error = cudaSuccess;
+    explicit DeviceGuard(int device) {
+        error = cudaGetDevice(&previous);
+        if (error == cudaSuccess && previous != device) {
+            error = cudaSetDevice(device);
+            switched = error == cudaSuccess;
+        }
+    }
+    ~DeviceGuard() {
+        if (switched) cudaSetDevice(previous);
+    }
+};
+
+inline bool aligned(const void* p, uintptr_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
+
+#define ZCK_REQUIRE(cond, ...) \
+    do {                       \
+        if (!(cond)) return ::zck::fail(ZCK_ERR_ARGUMENT, __VA_ARGS__); \
+    } while (0)
+
+#define ZCK_CUDA(call)                                                                                   \
+    do {                                                                                                 \
+        cudaError_t zck_e_ = (call);                                                                     \
+        if (zck_e_ != cudaSuccess)                                                                       \
+            return ::zck::fail(ZCK_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(zck_e_));       \
+    } while (0)
+
+// Hooks each kernel file provides for zck_init (shared-memory opt-in and the like).
+int init_gemm(int device);
+
+}  // namespace zck

@@ -1,0 +1,100 @@
+"""ctypes binding of libzck_b200.so (the C ABI declared in include/zck.h).
+
+The library is loaded on first use. A missing or unloadable library is an error on every path: nothing here falls
+back to PyTorch or to the CPU.
+"""
+
+import ctypes
+import os
+import pathlib
+import threading
+
+HERE = pathlib.Path(__file__).resolve().parent
+LIBRARY_NAME = "libzck_b200.so"
+
+BF16, F32, FP8_E4M3 = 0, 1, 2
+ACTIVATIONS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu": 3}
+WEIGHT_NONE, WEIGHT_BF16, WEIGHT_F32, WEIGHT_ZERO_CENTERED = 0, 1, 2, 4
+
+u32, u64, i32 = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int32
+ptr = ctypes.c_void_p
+
+
+class GemmSizes(ctypes.Structure):
+    """Mirror of `ZckGemmSizes`."""
+
+    _fields_ = [("a_stride", u64), ("b_stride", u64), ("sa_row", u64), ("sa_blk", u64), ("sb_row", u64),
+                ("sb_blk", u64), ("su_row", u64), ("su_blk", u64), ("out_stride", u64), ("residual_stride", u64),
+                ("m", u32), ("n", u32), ("k", u32), ("e8m0_bits", u32), ("activation", i32), ("splits", i32)]
+
+
+class Status(ctypes.Structure):
+    """Mirror of `ZckStatus`."""
+
+    _fields_ = [("code", u32), ("block", u32), ("stage", u32), ("count", u32)]
+
+
+SIGNATURES = {
+    "zck_init": (ctypes.c_int, [ctypes.c_int]),
+    "zck_last_error": (ctypes.c_char_p, []),
+    "zck_version": (ctypes.c_char_p, []),
+    "zck_quantize_fp8_rows": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, ptr, u64, ctypes.c_int, u32, u32,
+                                             ctypes.c_int, ptr]),
+    "zck_quantize_fp8_tiles": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, ptr, u64, ctypes.c_int, u32, u32,
+                                              ctypes.c_int, ptr]),
+    "zck_fused_add_rms_norm": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, u64, ptr, u64, ptr, ctypes.c_int, ptr, ptr,
+                                              ctypes.c_int, u64, u32, u32, ctypes.c_float, ctypes.c_int, ptr]),
+    "zck_gemm_plan": (ctypes.c_int, [ctypes.POINTER(GemmSizes), ctypes.c_int, ctypes.c_int,
+                                     ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(u32)]),
+    "zck_fp8_gemm": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes),
+                                    ctypes.c_int, ptr]),
+    "zck_fp8_gated_gemm": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr,
+                                          ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
+    "zck_poll_status": (ctypes.c_int, [ctypes.c_int, ctypes.POINTER(Status), ctypes.c_int]),
+}
+
+_library = None
+_lock = threading.Lock()
+
+
+def library_path():
+    return pathlib.Path(os.environ.get("ZCK_LIB") or HERE / LIBRARY_NAME)
+
+
+def library():
+    """Returns the loaded library with typed entry points; raises RuntimeError when it cannot be loaded."""
+    global _library
+    if _library is not None:
+        return _library
+    with _lock:
+        if _library is None:
+            path = library_path()
+            if not path.exists():
+                raise RuntimeError(f"{path} is missing: build it with `python zig-cu-kernels_b200/build.py` "
+                                   "(nvcc, sm_100a). zig_cu_kernels has no fallback path.")
+            loaded = ctypes.CDLL(str(path))
+            for name, (result, arguments) in SIGNATURES.items():
+                function = getattr(loaded, name)
+                function.restype, function.argtypes = result, arguments
+            _library = loaded
+    return _library
+
+
+class ZckError(RuntimeError):
+    pass
+
+
+def check(code):
+    """Turns a negative return code of a C call into the exception the op contract names."""
+    if code == 0:
+        return
+    message = library().zck_last_error().decode()
+    if code == -1:
+        raise ValueError(message)
+    raise ZckError(f"libzck_b200 failed with {code}: {message}")
+
+
+def poll_status(device, clear=False):
+    status = Status()
+    check(library().zck_poll_status(device, ctypes.byref(status), int(clear)))
+    return status

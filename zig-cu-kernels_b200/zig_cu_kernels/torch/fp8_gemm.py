@@ -1,0 +1,437 @@
+"""`fp8_gemm`, `fp8_gated_gemm`, `quantize_fp8_rows`, `quantize_fp8_tiles` as PyTorch custom ops over libzck_b200.
+
+Same schemas, output layouts, aliasing rules and errors as the reference's src/zig_cu_kernels/torch/fp8_gemm.py
+(:183-243 GEMM, :246-327 gated GEMM, :364-408 rows, :411-458 tiles); the part below the `run` seam is the C ABI.
+Only block128 scaling (one scale per row and 128 columns of the activation, one per 128 x 128 weight tile) is built;
+tensorwise and rowwise scale shapes are recognised and rejected with NotImplementedError.
+"""
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .common import (
+    GROUP,
+    KINDS,
+    SCALE_DTYPES,
+    block_scales_like,
+    need_below,
+    need_choice,
+    need_dtype,
+    raw_stream,
+    readable_rows,
+    row_matrix,
+    rows_of_leading,
+    workspace_for,
+    writable_rows,
+    writes_in_place,
+)
+from .ops import Out, Param, define
+
+__all__ = [
+    "quantize_fp8_rows", "quantize_fp8_tiles", "fp8_gemm", "fp8_gated_gemm",
+    "fp8_gemm_op", "fp8_gemm_out_op", "fp8_gated_gemm_op", "fp8_gated_gemm_out_op",
+    "quantize_fp8_rows_op", "quantize_fp8_rows_out_op", "quantize_fp8_tiles_op", "quantize_fp8_tiles_out_op",
+]
+
+FP8 = torch.float8_e4m3fn
+E8M0 = torch.float8_e8m0fnu
+BF16 = torch.bfloat16
+INPUT_DTYPES = (torch.bfloat16, torch.float32)
+ACTIVATIONS = tuple(_lib.ACTIVATIONS)
+LIMIT_32 = 1 << 32
+QUANTIZER_VALUES = 1 << 35
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# scaling type
+# --------------------------------------------------------------------------------------------------------------------
+
+def scaling_type(lead, columns, k, scale_a, weight_scales):
+    """Scaling type from the scale shapes, by the reference's rule (src/zig_cu_kernels/fp8_gemm.py:51-68): E8M0
+    scales of block shape are block128 first; then one-element scales are tensorwise, `(m,1)`/`(n,1)` rowwise, and the
+    block shapes block128."""
+    m = math.prod(lead)
+    groups = k // GROUP
+    a_shape = tuple(scale_a.shape)
+    w_shapes = [tuple(s.shape) for s in weight_scales]
+    block = a_shape in ((m, groups), (*lead, groups)) and all(s == (-(-columns // GROUP), groups) for s in w_shapes)
+    e8m0 = any(s.dtype == E8M0 for s in (scale_a, *weight_scales))
+    if e8m0 and block:
+        return "block128"
+    if math.prod(a_shape) == 1 and all(math.prod(s) == 1 for s in w_shapes):
+        return "tensorwise"
+    if a_shape in ((m, 1), (*lead, 1)) and all(s == (columns, 1) for s in w_shapes):
+        return "rowwise"
+    if block:
+        return "block128"
+    raise ValueError(f"the scale shapes {a_shape} and {', '.join(map(str, w_shapes))} match no scaling mode for "
+                     f"m = {m}, n = {columns} and k = {k}: tensorwise takes one-element scales, rowwise {(m, 1)} and "
+                     f"{(columns, 1)}, block128 {(m, groups)} and {(-(-columns // GROUP), groups)}")
+
+
+def check_product(a, weights, scale_a, weight_scales, use_fast_accum):
+    lead, k = tuple(a.shape[:-1]), a.shape[-1]
+    columns = next(iter(weights.values())).shape[0]
+    for name, weight in weights.items():
+        if tuple(weight.shape) != (columns, k):
+            raise ValueError(f"{name} must have the shape {(columns, k)}, got {tuple(weight.shape)}")
+    kind = scaling_type(lead, columns, k, scale_a, weight_scales)
+    e8m0 = any(s.dtype == E8M0 for s in (scale_a, *weight_scales))
+    if e8m0 and kind != "block128":
+        raise ValueError("E8M0 scales need block128 scaling")
+    multiple = GROUP if kind == "block128" else 16
+    if k <= 0 or k % multiple:
+        raise ValueError(f"{kind} scaling needs a positive k % {multiple} == 0")
+    if columns % 8:
+        raise ValueError("the weights need a row count that is a multiple of 8")
+    if use_fast_accum and kind == "block128":
+        raise ValueError("use_fast_accum does not take block128 scales")
+    need_below(LIMIT_32, m=math.prod(lead), n=columns, k=k)
+    if kind != "block128":
+        raise NotImplementedError(f"{kind} scaling is not built in this library yet; only block128 is")
+    return kind
+
+
+def scale_strides(scale, rows, groups, column_major_copy):
+    """`scale` (or a dense copy the kernel can stride over) with its (row, group) strides in elements; stride 0 for
+    an extent of 1."""
+    if scale.dim() > 2:
+        lead = rows_of_leading(scale)
+        flat = None if lead is None else (lead[1], scale.stride(-1))
+    else:
+        flat = (scale.stride(0), scale.stride(1))
+    aligned = scale.dtype != torch.float32 or scale.data_ptr() % 4 == 0
+    if flat is None or not aligned or min(flat) < 0:
+        copy = scale.new_empty((groups, rows)).t() if column_major_copy and groups > 1 else scale.new_empty((rows, groups))
+        copy.copy_(scale.reshape(rows, groups))
+        scale, flat = copy, (copy.stride(0), copy.stride(1))
+    return scale, (flat[0] if rows > 1 else 0, flat[1] if groups > 1 else 0)
+
+
+def bias_operand(bias):
+    if bias is None or (bias.is_contiguous() and bias.data_ptr() % 16 == 0):
+        return bias
+    return bias.clone(memory_format=torch.contiguous_format)
+
+
+def residual_operand(residual):
+    """Residual rows the kernel can read: in place when row-strided (stride 0 broadcasts one row), else a copy."""
+    if residual is None:
+        return None, 0
+    rows = row_matrix(residual)
+    if rows is None:
+        return readable_rows(residual)
+    return residual, rows[1]
+
+
+def output_target(out, inputs, residual):
+    """`out` when the kernel can write it in place (it may be the very view `residual`), else a contiguous
+    temporary that is copied back."""
+    if writable_rows(out) is not None and writes_in_place(out, inputs, aliases=(residual,)):
+        return out
+    return torch.empty(out.shape, dtype=out.dtype, device=out.device)
+
+
+def address(tensor):
+    return None if tensor is None else tensor.data_ptr()
+
+
+def launch_product(gated, device, sizes, pointers):
+    """Plans (K splits, workspace) and queues one GEMM launch on the current stream of `device`."""
+    lib = _lib.library()
+    part_bytes, counters = ctypes.c_size_t(0), ctypes.c_uint32(0)
+    _lib.check(lib.zck_gemm_plan(ctypes.byref(sizes), int(gated), device, ctypes.byref(part_bytes),
+                                 ctypes.byref(counters)))
+    stream = raw_stream(device)
+    entry = lib.zck_fp8_gated_gemm if gated else lib.zck_fp8_gemm
+    if part_bytes.value == 0:
+        _lib.check(entry(*pointers, None, None, ctypes.byref(sizes), device, stream))
+        return
+    with workspace_for(device, stream) as workspace:
+        parts, tile_counters = workspace.addresses(part_bytes.value, counters.value)
+        _lib.check(entry(*pointers, parts, tile_counters, ctypes.byref(sizes), device, stream))
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# fp8_gemm
+# --------------------------------------------------------------------------------------------------------------------
+
+def check_gemm(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum):
+    need_dtype("a", a, (FP8,))
+    need_dtype("b", b, (FP8,))
+    need_dtype("scale_a", scale_a, SCALE_DTYPES)
+    need_dtype("scale_b", scale_b, SCALE_DTYPES)
+    need_dtype("bias", bias, (BF16,))
+    need_dtype("residual", residual, (BF16,))
+    need_choice("activation", activation, ACTIVATIONS)
+    if a.dim() < 1 or b.dim() != 2:
+        raise ValueError("a must be [..., k], and b must be [n, k]")
+
+
+def check_gemm_sizes(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum):
+    check_product(a, {"b": b}, scale_a, (scale_b,), use_fast_accum)
+    n = b.shape[0]
+    if bias is not None and tuple(bias.shape) != (n,):
+        raise ValueError(f"bias must have the shape {(n,)}, got {tuple(bias.shape)}")
+    if residual is not None and tuple(residual.shape) != (*a.shape[:-1], n):
+        raise ValueError(f"residual must have the shape {(*a.shape[:-1], n)}, got {tuple(residual.shape)}")
+
+
+def gemm_output(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum):
+    return a.new_empty((*a.shape[:-1], b.shape[0]), dtype=BF16)
+
+
+def gemm_into(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum, out):
+    lead, (n, k) = tuple(a.shape[:-1]), b.shape
+    if tuple(out.shape) != (*lead, n):
+        raise ValueError(f"out must have the shape {(*lead, n)}, got {tuple(out.shape)}")
+    m = math.prod(lead)
+    if m == 0 or n == 0:
+        return
+    groups, tile_rows = k // GROUP, -(-n // GROUP)
+    target = output_target(out, (a, b, scale_a, scale_b, bias), residual)
+    (a, a_stride), (b, b_stride) = readable_rows(a), readable_rows(b)
+    scale_a, (sa_row, sa_blk) = scale_strides(scale_a, m, groups, True)
+    scale_b, (sb_row, sb_blk) = scale_strides(scale_b, tile_rows, groups, False)
+    bias = bias_operand(bias)
+    residual, residual_stride = residual_operand(residual)
+    e8m0 = (scale_a.dtype == E8M0) | ((scale_b.dtype == E8M0) << 1)
+    sizes = _lib.GemmSizes(a_stride=a_stride, b_stride=b_stride, sa_row=sa_row, sa_blk=sa_blk, sb_row=sb_row,
+                           sb_blk=sb_blk, su_row=0, su_blk=0, out_stride=writable_rows(target),
+                           residual_stride=residual_stride, m=m, n=n, k=k, e8m0_bits=e8m0,
+                           activation=_lib.ACTIVATIONS[activation], splits=1)
+    pointers = (a.data_ptr(), b.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), target.data_ptr(), address(bias),
+                address(residual))
+    launch_product(False, a.get_device(), sizes, pointers)
+    if target is not out:
+        out.copy_(target)
+
+
+FP8_GEMM = define(
+    "fp8_gemm",
+    params=[Param("Tensor", "a"), Param("Tensor", "b"), Param("Tensor", "scale_a"), Param("Tensor", "scale_b"),
+            Param("Tensor?", "bias"), Param("Tensor?", "residual"), Param("str", "activation"),
+            Param("bool", "use_fast_accum")],
+    outs=[Out("out", "out", gemm_output, BF16)], check=check_gemm, check_sizes=check_gemm_sizes, run=gemm_into)
+fp8_gemm_op, fp8_gemm_out_op = FP8_GEMM.functional, FP8_GEMM.out
+
+
+def fp8_gemm(a, b, scale_a, scale_b, *, bias=None, activation="none", residual=None, use_fast_accum=False, out=None):
+    """BF16 `act(a_deq @ b_deq.T + bias) + residual` of the E4M3 activation `a [..., k]` and weight `b [n, k]` with
+    block128 scales `scale_a (m, k/128)` and `scale_b (ceil(n/128), k/128)`, FP32 or E8M0. `residual` may be `out`."""
+    return FP8_GEMM(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum, outputs={"out": out})
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# fp8_gated_gemm
+# --------------------------------------------------------------------------------------------------------------------
+
+def check_gated(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up, residual, activation,
+                use_fast_accum):
+    for name, tensor in (("a", a), ("w_gate", w_gate), ("w_up", w_up)):
+        need_dtype(name, tensor, (FP8,))
+    for name, tensor in (("scale_a", scale_a), ("scale_gate", scale_gate), ("scale_up", scale_up)):
+        need_dtype(name, tensor, SCALE_DTYPES)
+    for name, tensor in (("bias_gate", bias_gate), ("bias_up", bias_up), ("residual", residual)):
+        need_dtype(name, tensor, (BF16,))
+    need_choice("activation", activation, ACTIVATIONS)
+    if a.dim() < 1 or w_gate.dim() != 2 or w_up.dim() != 2:
+        raise ValueError("a must be [..., k], and w_gate and w_up must be [f, k]")
+
+
+def check_gated_sizes(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up, residual, activation,
+                      use_fast_accum):
+    check_product(a, {"w_gate": w_gate, "w_up": w_up}, scale_a, (scale_gate, scale_up), use_fast_accum)
+    f = w_gate.shape[0]
+    for name, bias in (("bias_gate", bias_gate), ("bias_up", bias_up)):
+        if bias is not None and tuple(bias.shape) != (f,):
+            raise ValueError(f"{name} must have the shape {(f,)}, got {tuple(bias.shape)}")
+    if residual is not None and tuple(residual.shape) != (*a.shape[:-1], f):
+        raise ValueError(f"residual must have the shape {(*a.shape[:-1], f)}, got {tuple(residual.shape)}")
+
+
+def gated_output(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up, residual, activation,
+                 use_fast_accum):
+    return a.new_empty((*a.shape[:-1], w_gate.shape[0]), dtype=BF16)
+
+
+def gated_into(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up, residual, activation,
+               use_fast_accum, out):
+    lead, (f, k) = tuple(a.shape[:-1]), w_gate.shape
+    if tuple(out.shape) != (*lead, f):
+        raise ValueError(f"out must have the shape {(*lead, f)}, got {tuple(out.shape)}")
+    m = math.prod(lead)
+    if m == 0 or f == 0:
+        return
+    groups, tile_rows = k // GROUP, -(-f // GROUP)
+    target = output_target(out, (a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up), residual)
+    a, a_stride = readable_rows(a)
+    (gate, gate_stride), (up, up_stride) = readable_rows(w_gate), readable_rows(w_up)
+    if gate_stride != up_stride and f > 1:  # the kernel reads both weights with one row stride
+        gate, up = gate.contiguous(), up.contiguous()
+        gate_stride = k
+    scale_a, (sa_row, sa_blk) = scale_strides(scale_a, m, groups, True)
+    scale_gate, (sg_row, sg_blk) = scale_strides(scale_gate, tile_rows, groups, False)
+    scale_up, (su_row, su_blk) = scale_strides(scale_up, tile_rows, groups, False)
+    bias_gate, bias_up = bias_operand(bias_gate), bias_operand(bias_up)
+    residual, residual_stride = residual_operand(residual)
+    e8m0 = (scale_a.dtype == E8M0) | ((scale_gate.dtype == E8M0) << 1) | ((scale_up.dtype == E8M0) << 2)
+    sizes = _lib.GemmSizes(a_stride=a_stride, b_stride=gate_stride, sa_row=sa_row, sa_blk=sa_blk, sb_row=sg_row,
+                           sb_blk=sg_blk, su_row=su_row, su_blk=su_blk, out_stride=writable_rows(target),
+                           residual_stride=residual_stride, m=m, n=f, k=k, e8m0_bits=e8m0,
+                           activation=_lib.ACTIVATIONS[activation], splits=1)
+    pointers = (a.data_ptr(), gate.data_ptr(), up.data_ptr(), scale_a.data_ptr(), scale_gate.data_ptr(),
+                scale_up.data_ptr(), target.data_ptr(), address(bias_gate), address(bias_up), address(residual))
+    launch_product(True, a.get_device(), sizes, pointers)
+    if target is not out:
+        out.copy_(target)
+
+
+FP8_GATED_GEMM = define(
+    "fp8_gated_gemm",
+    params=[Param("Tensor", "a"), Param("Tensor", "w_gate"), Param("Tensor", "w_up"), Param("Tensor", "scale_a"),
+            Param("Tensor", "scale_gate"), Param("Tensor", "scale_up"), Param("Tensor?", "bias_gate"),
+            Param("Tensor?", "bias_up"), Param("Tensor?", "residual"), Param("str", "activation"),
+            Param("bool", "use_fast_accum")],
+    outs=[Out("out", "out", gated_output, BF16)], check=check_gated, check_sizes=check_gated_sizes, run=gated_into)
+fp8_gated_gemm_op, fp8_gated_gemm_out_op = FP8_GATED_GEMM.functional, FP8_GATED_GEMM.out
+
+
+def fp8_gated_gemm(a, w_gate, w_up, scale_a, scale_gate, scale_up, *, bias_gate=None, bias_up=None, activation="silu",
+                   residual=None, use_fast_accum=False, out=None):
+    """BF16 `act(a w_gate^T + bias_gate) * (a w_up^T + bias_up) [+ residual]` with block128 scales; `w_gate` and
+    `w_up` are `[f, k]` (they may be the halves of one `[2f, k]` tensor)."""
+    return FP8_GATED_GEMM(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up, residual, activation,
+                          use_fast_accum, outputs={"out": out})
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# quantizers
+# --------------------------------------------------------------------------------------------------------------------
+
+def check_quantizer(name, x, scale_dtype):
+    need_dtype(name, x, INPUT_DTYPES)
+    if x.dim() < 1:
+        raise ValueError(f"{name} needs at least one dimension")
+    need_choice("scale_dtype", scale_dtype, SCALE_DTYPES)
+
+
+def check_quantizer_sizes(name, x):
+    need_below(QUANTIZER_VALUES, **{f"{name}.numel()": x.numel()})
+    need_below(LIMIT_32, **{f"the rows of {name}": math.prod(x.shape[:-1]), f"{name}.shape[-1]": x.shape[-1]})
+    if x.shape[-1] % GROUP:
+        raise ValueError(f"{name} needs a last dimension that is a multiple of {GROUP}, got {x.shape[-1]}")
+
+
+def codes_target(q, inputs):
+    if q.is_contiguous() and q.data_ptr() % 8 == 0 and writes_in_place(q, inputs):
+        return q
+    return torch.empty(q.shape, dtype=FP8, device=q.device)
+
+
+def check_rows(x, scale_dtype):
+    check_quantizer("x", x, scale_dtype)
+
+
+def check_rows_sizes(x, scale_dtype):
+    check_quantizer_sizes("x", x)
+
+
+def rows_codes(x, scale_dtype):
+    return x.new_empty(x.shape, dtype=FP8)
+
+
+def rows_scales(x, scale_dtype):
+    return block_scales_like(x, scale_dtype)
+
+
+def rows_into(x, q, scales):
+    m, k = math.prod(x.shape[:-1]), x.shape[-1]
+    if tuple(q.shape) != tuple(x.shape) or tuple(scales.shape) != (m, k // GROUP):
+        raise ValueError(f"q must have the shape {tuple(x.shape)} and scales {(m, k // GROUP)}")
+    if m * k == 0:
+        return
+    source, stride = readable_rows(x)
+    codes = codes_target(q, (x,))
+    direct = ((m <= 1 or scales.stride(0) == 1) and (k <= GROUP or scales.stride(1) >= m) and
+              writes_in_place(scales, (x,)) and (scales.dtype == E8M0 or scales.data_ptr() % 4 == 0))
+    targets = scales if direct else block_scales_like(x, scales.dtype)
+    group_stride = targets.stride(1) if k > GROUP else m
+    device = x.get_device()
+    _lib.check(_lib.library().zck_quantize_fp8_rows(
+        source.data_ptr(), KINDS[x.dtype], stride, codes.data_ptr(), targets.data_ptr(), group_stride,
+        int(scales.dtype == E8M0), m, k, device, raw_stream(device)))
+    if codes is not q:
+        q.copy_(codes)
+    if targets is not scales:
+        scales.copy_(targets)
+
+
+QUANTIZE_FP8_ROWS = define(
+    "quantize_fp8_rows", params=[Param("Tensor", "x"), Param("ScalarType", "scale_dtype")],
+    outs=[Out("q", "out", rows_codes, FP8), Out("scales", "scales_out", rows_scales, "scale_dtype")],
+    check=check_rows, check_sizes=check_rows_sizes, run=rows_into)
+quantize_fp8_rows_op, quantize_fp8_rows_out_op = QUANTIZE_FP8_ROWS.functional, QUANTIZE_FP8_ROWS.out
+
+
+def quantize_fp8_rows(x, *, scale_dtype=torch.float32, out=None, scales_out=None):
+    """E4M3 codes of `x [..., k]` and one scale per row and 128 values: `(q, scales)` with `scales (m, k/128)` of
+    strides `(1, m)`, ready to be the `a`, `scale_a` of `fp8_gemm`."""
+    return QUANTIZE_FP8_ROWS(x, scale_dtype, outputs={"out": out, "scales_out": scales_out})
+
+
+def check_tiles(w, scale_dtype):
+    check_quantizer("w", w, scale_dtype)
+    if w.dim() != 2:
+        raise ValueError("w must be an [n, k] matrix")
+
+
+def check_tiles_sizes(w, scale_dtype):
+    check_quantizer_sizes("w", w)
+
+
+def tiles_codes(w, scale_dtype):
+    return w.new_empty(w.shape, dtype=FP8)
+
+
+def tiles_scales(w, scale_dtype):
+    return w.new_empty((-(-w.shape[0] // GROUP), w.shape[-1] // GROUP), dtype=scale_dtype)
+
+
+def tiles_into(w, q, scales):
+    (n, k), tile_rows = w.shape, -(-w.shape[0] // GROUP)
+    if tuple(q.shape) != (n, k) or tuple(scales.shape) != (tile_rows, k // GROUP):
+        raise ValueError(f"q must have the shape {(n, k)} and scales {(tile_rows, k // GROUP)}")
+    if n * k == 0:
+        return
+    source, stride = readable_rows(w)
+    codes = codes_target(q, (w,))
+    direct = ((k <= GROUP or scales.stride(1) == 1) and (tile_rows <= 1 or scales.stride(0) >= k // GROUP) and
+              writes_in_place(scales, (w,)) and (scales.dtype == E8M0 or scales.data_ptr() % 4 == 0))
+    targets = scales if direct else torch.empty(scales.shape, dtype=scales.dtype, device=scales.device)
+    row_stride = targets.stride(0) if tile_rows > 1 else k // GROUP
+    device = w.get_device()
+    _lib.check(_lib.library().zck_quantize_fp8_tiles(
+        source.data_ptr(), KINDS[w.dtype], stride, codes.data_ptr(), targets.data_ptr(), row_stride,
+        int(scales.dtype == E8M0), n, k, device, raw_stream(device)))
+    if codes is not q:
+        q.copy_(codes)
+    if targets is not scales:
+        scales.copy_(targets)
+
+
+QUANTIZE_FP8_TILES = define(
+    "quantize_fp8_tiles", params=[Param("Tensor", "w"), Param("ScalarType", "scale_dtype")],
+    outs=[Out("q", "out", tiles_codes, FP8), Out("scales", "scales_out", tiles_scales, "scale_dtype")],
+    check=check_tiles, check_sizes=check_tiles_sizes, run=tiles_into)
+quantize_fp8_tiles_op, quantize_fp8_tiles_out_op = QUANTIZE_FP8_TILES.functional, QUANTIZE_FP8_TILES.out
+
+
+def quantize_fp8_tiles(w, *, scale_dtype=torch.float32, out=None, scales_out=None):
+    """E4M3 codes of the weight `w [n, k]` and one scale per 128 x 128 tile: `(q, scales)` with contiguous
+    `scales (ceil(n/128), k/128)`, ready to be the `b`, `scale_b` of `fp8_gemm`."""
+    return QUANTIZE_FP8_TILES(w, scale_dtype, outputs={"out": out, "scales_out": scales_out})

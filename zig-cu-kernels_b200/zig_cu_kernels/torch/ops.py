@@ -1,0 +1,253 @@
+"""Registration of an op pair `<name>` / `<name>_out` in `torch.ops.zig_cu_kernels`.
+
+Keeps the contract of the reference's `define` (src/zig_cu_kernels/torch/ops.py:127-142, :267-272): both ops carry
+`pt2_compliant_tag`, a CUDA kernel, a fake kernel (shape/dtype checks only, so tracing adds no size guards) and an
+Autograd kernel that lets the forward run and raises on backward. The functional op allocates its outputs; the
+`_out` op writes the given ones and returns nothing. Schemas are spelled out by the caller instead of being inferred.
+"""
+
+import torch
+
+from .. import _lib
+from .common import common_cuda_device, fp32_scalar, need_separate_outputs, need_tensor, python_int, same_device
+
+NAMESPACE = "zig_cu_kernels"
+E8M0 = torch.float8_e8m0fnu
+_libraries = {}
+
+
+def _library(namespace):
+    if namespace not in _libraries:
+        _libraries[namespace] = torch.library.Library(namespace, "FRAGMENT")
+    return _libraries[namespace]
+
+
+class Param:
+    """One parameter of the functional op: schema type (`Tensor`, `Tensor?`, `float`, `int`, `bool`, `str`,
+    `ScalarType`) and name."""
+
+    def __init__(self, kind, name):
+        self.kind, self.name = kind, name
+        self.is_tensor = kind.startswith("Tensor")
+        self.optional = kind.endswith("?")
+
+
+class Out:
+    """One output: name in the `_out` schema, keyword of the public function, allocator taking the functional
+    arguments, and its dtype rule: a `torch.dtype`, the name of a tensor parameter (same dtype), the name of a
+    `ScalarType` parameter (which the `_out` op then reads from this output), or a function of the arguments."""
+
+    def __init__(self, name, keyword, allocate, dtype):
+        self.name, self.keyword, self.allocate, self.dtype = name, keyword, allocate, dtype
+
+
+class NoBackward(torch.autograd.Function):
+    """Lets inference code call the ops on tensors that require grad; differentiating through them is an error."""
+
+    @staticmethod
+    def forward(ctx, op, name, *arguments):
+        ctx.name = name
+        with torch._C._AutoDispatchBelowAutograd():
+            return op(*arguments)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise RuntimeError(f"zig_cu_kernels::{ctx.name} is an inference op and has no backward formula")
+
+
+class OpPair:
+    def __init__(self, name, params, outs, check, check_sizes, run, namespace=NAMESPACE):
+        self.name, self.params, self.outs = name, params, outs
+        self.check, self.check_sizes, self.run = check, check_sizes, run
+        self.names = [p.name for p in params]
+        # ScalarType parameters exist only on the functional op; the `_out` op reads them from an output's dtype.
+        self.dtype_params = {p.name for p in params if p.kind == "ScalarType"}
+        self.input_positions = [i for i, p in enumerate(params) if p.name not in self.dtype_params]
+        self.dtype_source = {}
+        for index, out in enumerate(outs):
+            if isinstance(out.dtype, str) and out.dtype in self.dtype_params:
+                self.dtype_source.setdefault(out.dtype, index)
+        missing = self.dtype_params - set(self.dtype_source)
+        if missing:
+            raise ValueError(f"{name}: no output defines the dtype parameter(s) {sorted(missing)}")
+        self.tensor_positions = [i for i, p in enumerate(params) if p.is_tensor]
+        if not self.tensor_positions or params[self.tensor_positions[0]].optional:
+            raise ValueError(f"{name}: the first tensor parameter must be required")
+        self.keywords = [out.keyword for out in outs]
+        self._register(namespace)
+
+    # ---- schemas and registration ------------------------------------------------------------------------------
+    def _register(self, namespace):
+        functional_args = ", ".join(f"{p.kind} {p.name}" for p in self.params)
+        returns = "Tensor" if len(self.outs) == 1 else "(" + ", ".join(["Tensor"] * len(self.outs)) + ")"
+        inputs = [self.params[i] for i in self.input_positions]
+        out_args = [f"{p.kind} {p.name}" for p in inputs]
+        out_args += [f"Tensor(a{len(inputs) + i}!) {out.name}" for i, out in enumerate(self.outs)]
+        library = _library(namespace)
+        tags = (torch.Tag.pt2_compliant_tag,)
+        library.define(f"{self.name}({functional_args}) -> {returns}", tags=tags)
+        library.define(f"{self.name}_out({', '.join(out_args)}) -> ()", tags=tags)
+        library.impl(self.name, self._functional_cuda, "CUDA")
+        library.impl(f"{self.name}_out", self._out_cuda, "CUDA")
+        torch.library.register_fake(f"{namespace}::{self.name}", self._functional_fake, lib=library)
+        torch.library.register_fake(f"{namespace}::{self.name}_out", self._out_fake, lib=library)
+        packet = getattr(torch.ops, namespace)
+        self.functional = getattr(packet, self.name).default
+        self.out = getattr(packet, f"{self.name}_out").default
+        library.impl(self.name, self._functional_autograd, "Autograd")
+        library.impl(f"{self.name}_out", self._out_autograd, "Autograd")
+
+    # ---- helpers -----------------------------------------------------------------------------------------------
+    def _named_tensors(self, arguments):
+        return [(self.names[i], arguments[i]) for i in self.tensor_positions]
+
+    def _allocate(self, arguments):
+        results = tuple(out.allocate(*arguments) for out in self.outs)
+        return results[0] if len(results) == 1 else results
+
+    def _expected_dtype(self, out, functional_arguments):
+        rule = out.dtype
+        if isinstance(rule, torch.dtype):
+            return rule
+        if callable(rule):
+            return rule(*functional_arguments)
+        value = functional_arguments[self.names.index(rule)]
+        return value if isinstance(value, torch.dtype) else value.dtype
+
+    def _functional_arguments(self, out_arguments):
+        """Arguments of the functional op for the arguments of the `_out` op; checks the dtypes of the outputs."""
+        count = len(self.input_positions)
+        inputs, outputs = out_arguments[:count], out_arguments[count:]
+        arguments = [None] * len(self.params)
+        for position, value in zip(self.input_positions, inputs):
+            arguments[position] = value
+        for name, index in self.dtype_source.items():
+            arguments[self.names.index(name)] = outputs[index].dtype
+        for out, tensor in zip(self.outs, outputs):
+            expected = self._expected_dtype(out, arguments)
+            if tensor.dtype != expected:
+                raise ValueError(f"{out.name} must be a {expected} tensor, got {tensor.dtype}")
+        return arguments
+
+    # ---- kernels -----------------------------------------------------------------------------------------------
+    @torch._disable_dynamo
+    def _functional_cuda(self, *arguments):
+        device = common_cuda_device(self._named_tensors(arguments))
+        self.check(*arguments)
+        if self.check_sizes is not None:
+            self.check_sizes(*arguments)
+        _lib.check(_lib.library().zck_init(device))
+        outputs = self._allocate(arguments)
+        inputs = [arguments[i] for i in self.input_positions]
+        self.run(*inputs, *(outputs if isinstance(outputs, tuple) else (outputs,)))
+        return outputs
+
+    def _functional_fake(self, *arguments):
+        same_device(self._named_tensors(arguments))
+        self.check(*arguments)
+        return self._allocate(arguments)
+
+    @torch._disable_dynamo
+    def _out_cuda(self, *arguments):
+        count = len(self.input_positions)
+        named = [(self.params[p].name, arguments[i]) for i, p in enumerate(self.input_positions)
+                 if self.params[p].is_tensor]
+        named += [(out.name, arguments[count + i]) for i, out in enumerate(self.outs)]
+        device = common_cuda_device(named)
+        functional = self._functional_arguments(arguments)
+        self.check(*functional)
+        if self.check_sizes is not None:
+            self.check_sizes(*functional)
+        need_separate_outputs([out.name for out in self.outs], arguments[count:])
+        _lib.check(_lib.library().zck_init(device))
+        self.run(*arguments)
+
+    def _out_fake(self, *arguments):
+        count = len(self.input_positions)
+        named = [(self.params[p].name, arguments[i]) for i, p in enumerate(self.input_positions)
+                 if self.params[p].is_tensor]
+        named += [(out.name, arguments[count + i]) for i, out in enumerate(self.outs)]
+        same_device(named)
+        self.check(*self._functional_arguments(arguments))
+
+    def _functional_autograd(self, *arguments):
+        needs_grad = torch.is_grad_enabled() and any(
+            isinstance(a, torch.Tensor) and a.requires_grad for a in arguments)
+        if needs_grad:
+            return NoBackward.apply(self.functional, self.name, *arguments)
+        with torch._C._AutoDispatchBelowAutograd():
+            return self.functional(*arguments)
+
+    def _out_autograd(self, *arguments):
+        torch._C._increment_version(list(arguments[len(self.input_positions):]))
+        with torch._C._AutoDispatchBelowAutograd():
+            return self.out(*arguments)
+
+    # ---- public call -------------------------------------------------------------------------------------------
+    def _checked(self, arguments):
+        if len(arguments) != len(self.params):
+            raise TypeError(f"{self.name} takes {len(self.params)} arguments, got {len(arguments)}")
+        checked = list(arguments)
+        for index, param in enumerate(self.params):
+            value = checked[index]
+            if value is None and param.optional:
+                continue
+            if param.is_tensor:
+                need_tensor(param.name, value)
+            elif param.kind == "float":
+                checked[index] = fp32_scalar(param.name, value)
+            elif param.kind.startswith("int"):
+                checked[index] = python_int(param.name, value)
+        return checked
+
+    def __call__(self, *arguments, outputs=None):
+        """Calls the functional op when no output tensor is given, else the `_out` op (allocating the outputs that
+        were not given). Under `torch.compile`, a call that involves an E8M0 tensor or dtype runs the functional op
+        and copies, because Inductor cannot yet lower a mutating custom op with a `float8_e8m0fnu` argument."""
+        arguments = self._checked(arguments)
+        outputs = outputs or {}
+        for keyword in outputs:
+            if keyword not in self.keywords:
+                raise TypeError(f"{self.name} has no output {keyword}")
+        given = [outputs.get(keyword) for keyword in self.keywords]
+        for keyword, tensor in zip(self.keywords, given):
+            if tensor is not None:
+                need_tensor(keyword, tensor)
+        if all(tensor is None for tensor in given):
+            return self.functional(*arguments)
+        for name, index in self.dtype_source.items():
+            wanted = arguments[self.names.index(name)]
+            if given[index] is not None and given[index].dtype != wanted:
+                raise ValueError(f"{self.keywords[index]} must be a {wanted} tensor, got {given[index].dtype}")
+        compiling = torch.compiler.is_compiling()
+        if compiling and any((isinstance(v, torch.Tensor) and v.dtype == E8M0) or v is E8M0
+                             for v in (*arguments, *given)):
+            return self._copy_results(arguments, given)
+        if any(tensor is None for tensor in given):
+            if not compiling:
+                self.check(*arguments)
+            given = [tensor if tensor is not None else out.allocate(*arguments)
+                     for out, tensor in zip(self.outs, given)]
+        self.out(*(arguments[i] for i in self.input_positions), *given)
+        return given[0] if len(given) == 1 else tuple(given)
+
+    def _copy_results(self, arguments, given):
+        results = self.functional(*arguments)
+        results = (results,) if len(self.outs) == 1 else results
+        final = []
+        for keyword, target, result in zip(self.keywords, given, results):
+            if target is None:
+                final.append(result)
+                continue
+            if target.dtype != result.dtype or target.shape != result.shape:
+                raise ValueError(f"{keyword} must be a {result.dtype} tensor of the shape {tuple(result.shape)}")
+            target.copy_(result)
+            final.append(target)
+        return final[0] if len(final) == 1 else tuple(final)
+
+
+def define(name, *, params, outs, check, run, check_sizes=None, namespace=NAMESPACE):
+    """Registers `name` and `name_out`. `params` lists `Param`s of the functional op, `outs` the `Out`s.
+    `check(*functional_args)` validates dtypes and ranks (it also runs on fake tensors); `check_sizes` validates
+    concrete sizes (real tensors only, before any allocation); `run(*inputs, *outputs)` queues the kernels."""
+    return OpPair(name, params, outs, check, check_sizes, run, namespace)
