@@ -1,0 +1,343 @@
+"""fp8_gemm / fp8_gated_gemm on the GPU.
+
+Tolerance of the hot path: max relative error 1e-2 against the FP32 dequantise-and-matmul (BF16 output, FP32
+accumulate). On top of it the reference's tighter per-element bound |out - exact| <= 1.01 * (2^-9 * sum|A||B| +
+2^-8 * |y| ...) (tests/test_fp8_gemm.py:165-199, :436-465 of the reference) and its bitwise cases: exact operands,
+every BF16 pattern through the epilogue, E8M0 scales equal to their FP32 values.
+"""
+
+import itertools
+
+import pytest
+import torch
+
+from helpers import BF16, E8M0, FP8, assert_same_bits, from_golden, max_relative_error
+from oracle import rules
+
+pytestmark = pytest.mark.gpu
+ACTIVATIONS = ("none", "silu", "gelu_tanh", "gelu")
+TOLERANCE = 1e-2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import zig_cu_kernels.torch as z
+    return z
+
+
+def column_major(values):
+    """`values (m, groups)` in the layout the row quantizer produces: strides (1, m)."""
+    out = torch.empty(values.shape[::-1], dtype=values.dtype, device=values.device).t()
+    out.copy_(values)
+    return out
+
+
+def check_bound(out, reference, allowed, name):
+    out = out.double().reshape(reference.shape)
+    error = torch.where(out == reference, 0.0, (out - reference).abs())
+    limit = 1.01 * allowed
+    worst = float(torch.where(error <= limit, 0.0, error / limit).max())
+    assert worst == 0.0, f"{name}: largest error / bound = {worst}"
+
+
+def test_config1_matches_the_reference_product(ops, golden):
+    g = golden["gemm"]
+    a, b = from_golden(g["c1_a"], FP8).cuda(), from_golden(g["c1_b"], FP8).cuda()
+    scale_a = column_major(from_golden(g["c1_scale_a"], torch.float32).cuda())
+    scale_b = from_golden(g["c1_scale_b"], torch.float32).cuda()
+    out = ops.fp8_gemm(a, b, scale_a, scale_b)
+    assert out.shape == (256, 512) and out.dtype == BF16
+    for key in ("c1_out_fp64_path", "c1_out_fp32_path"):
+        reference = from_golden(g[key], BF16)
+        assert max_relative_error(out, reference) <= TOLERANCE
+        # elementwise: at most one BF16 step plus the accumulation allowance away from the reference's output
+        difference = (out.cpu().float() - reference.float()).abs()
+        assert float((difference / reference.float().abs().clamp_min(2.0**-6)).max()) <= 2.0**-6
+    s, error = rules.error_terms(a.cpu(), scale_a.cpu(), b.cpu(), scale_b.cpu())
+    check_bound(out.cpu(), *rules.store_bound(s, error, None, "none", None), "config 1")
+
+
+def test_config1_end_to_end_from_bf16(ops, golden):
+    """Quantize the seeded BF16 inputs on the GPU: codes and scales equal the golden ones, then the product."""
+    g = golden["gemm"]
+    generator = torch.Generator().manual_seed(0)
+    a_hp = torch.randn(256, 1024, generator=generator).bfloat16().cuda()
+    b_hp = (torch.randn(512, 1024, generator=generator) / 32).bfloat16().cuda()
+    a, scale_a = ops.quantize_fp8_rows(a_hp)
+    b, scale_b = ops.quantize_fp8_tiles(b_hp)
+    assert_same_bits(a, from_golden(g["c1_a"], FP8), "a")
+    assert_same_bits(b, from_golden(g["c1_b"], FP8), "b")
+    assert_same_bits(scale_a, from_golden(g["c1_scale_a"], torch.float32), "scale_a")
+    assert_same_bits(scale_b, from_golden(g["c1_scale_b"], torch.float32), "scale_b")
+    out = ops.fp8_gemm(a, b, scale_a, scale_b)
+    assert max_relative_error(out, from_golden(g["c1_out_fp64_path"], BF16)) <= TOLERANCE
+
+
+def exact_tensors(golden):
+    g = golden["gemm"]
+    names = (("a", FP8), ("b", FP8), ("up", FP8), ("scale_a", torch.float32), ("scale_b", torch.float32),
+             ("scale_up", torch.float32), ("bias", BF16), ("bias_up", BF16), ("residual", BF16), ("s", torch.float32),
+             ("s_up", torch.float32))
+    return {name: from_golden(g[f"ep_{name}"], dtype).cuda() for name, dtype in names}
+
+
+def test_exact_operands_are_bitwise(ops, golden):
+    """Codes in {-1,0,1} and power-of-two scales make every partial sum exact, so any accumulation order gives the
+    bits of the BF16 epilogue sequence. m=70, n=264, k=640: partial tiles in M and N."""
+    g, t = golden["gemm"], exact_tensors(golden)
+    scale_a = column_major(t["scale_a"])
+    out = ops.fp8_gemm(t["a"], t["b"], scale_a, t["scale_b"], bias=t["bias"], residual=t["residual"])
+    assert_same_bits(out, from_golden(g["ep_store_none"], BF16), "store vs golden")
+    out = ops.fp8_gemm(t["a"], t["b"], scale_a, t["scale_b"])
+    assert_same_bits(out, from_golden(g["ep_store_none_plain"], BF16), "plain vs golden")
+    out = ops.fp8_gated_gemm(t["a"], t["b"], t["up"], scale_a, t["scale_b"], t["scale_up"], bias_gate=t["bias"],
+                             bias_up=t["bias_up"], activation="none", residual=t["residual"])
+    assert_same_bits(out, from_golden(g["ep_gated_none"], BF16), "gated vs golden")
+    # every activation against PyTorch's own BF16 CUDA ops on the exact sums (row-major scale_a this time)
+    for activation, with_bias, with_residual in itertools.product(ACTIVATIONS, (False, True), (False, True)):
+        bias = t["bias"] if with_bias else None
+        residual = t["residual"] if with_residual else None
+        out = ops.fp8_gemm(t["a"], t["b"], t["scale_a"], t["scale_b"], bias=bias, activation=activation, residual=residual)
+        assert_same_bits(out, rules.store_epilogue(t["s"], bias, activation, residual), f"store {activation}")
+        out = ops.fp8_gated_gemm(t["a"], t["b"], t["up"], t["scale_a"], t["scale_b"], t["scale_up"], bias_gate=bias,
+                                 bias_up=t["bias_up"] if with_bias else None, activation=activation, residual=residual)
+        expected = rules.gated_epilogue(t["s"], t["s_up"], bias, t["bias_up"] if with_bias else None, activation, residual)
+        assert_same_bits(out, expected, f"gated {activation}")
+
+
+def exact_operands(m, n, k, generator, e8m0=False):
+    a = torch.randint(-1, 2, (m, k), device="cuda", generator=generator).float().to(FP8)
+    b = torch.randint(-1, 2, (n, k), device="cuda", generator=generator).float().to(FP8)
+    blocks = torch.arange(k // 128, device="cuda")
+    row = torch.randint(-3, 4, (m, 1), device="cuda", generator=generator)
+    tile = torch.randint(-2, 3, (-(-n // 128), 1), device="cuda", generator=generator)
+    a_exp, b_exp = row - blocks[None, :] % 4, tile - blocks[None, :] % 2
+    if e8m0:
+        return a, b, column_major((a_exp + 127).to(torch.uint8).view(E8M0)), (b_exp + 127).to(torch.uint8).view(E8M0)
+    return a, b, column_major(torch.exp2(a_exp.float())), torch.exp2(b_exp.float())
+
+
+@pytest.mark.parametrize("m,n,k", [(70, 384, 1024), (16, 4096, 2048), (129, 136, 1024), (1, 8, 128), (300, 520, 512)])
+def test_exact_operands_are_bitwise_with_split_k_and_odd_shapes(ops, m, n, k):
+    """Few tiles and deep K make the plan split K; the fixed-order reduction keeps exact sums exact."""
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    for e8m0 in (False, True):
+        a, b, scale_a, scale_b = exact_operands(m, n, k, generator, e8m0)
+        _, up, _, scale_up = exact_operands(m, n, k, generator, e8m0)
+        bias = torch.randn(n, device="cuda", generator=generator).bfloat16()
+        residual = torch.randn(m, n, device="cuda", generator=generator).bfloat16()
+        s = rules.block_sums(a.cpu(), scale_a.cpu(), b.cpu(), scale_b.cpu()).float().cuda()
+        s_up = rules.block_sums(a.cpu(), scale_a.cpu(), up.cpu(), scale_up.cpu()).float().cuda()
+        for _ in range(2):  # the second call finds the counters back at zero
+            out = ops.fp8_gemm(a, b, scale_a, scale_b, bias=bias, activation="silu", residual=residual)
+            assert_same_bits(out, rules.store_epilogue(s, bias, "silu", residual), f"store e8m0={e8m0}")
+            out = ops.fp8_gated_gemm(a, b, up, scale_a, scale_b, scale_up, bias_up=bias)
+            assert_same_bits(out, rules.gated_epilogue(s, s_up, None, bias, "silu", None), f"gated e8m0={e8m0}")
+    from zig_cu_kernels.torch import common
+    for workspace in common._eager.values():
+        assert bool(workspace.counters.eq(0).all()), "the tile counters must be left at zero"
+
+
+def test_every_bf16_pattern_through_the_epilogue(ops):
+    """Zero sums with all 65536 BF16 bit patterns as bias, gate bias and residual give the bits of PyTorch's BF16
+    CUDA ops (tests/test_fp8_gemm.py:580-611 of the reference)."""
+    generator = torch.Generator(device="cuda").manual_seed(13)
+    patterns = torch.arange(-(1 << 15), 1 << 15, dtype=torch.int32).to(torch.int16).view(BF16).cuda()
+    m, n, k = 4, patterns.numel(), 128
+    zeros_a, zeros_b = torch.zeros(m, k, device="cuda").to(FP8), torch.zeros(n, k, device="cuda").to(FP8)
+    scale_a = column_major(torch.ones(m, 1, device="cuda"))
+    scale_b = torch.ones(n // 128, 1, device="cuda")
+    residual = torch.stack([patterns[torch.randperm(n, device="cuda", generator=generator)] for _ in range(m)])
+    bias_up = patterns[torch.randperm(n, device="cuda", generator=generator)]
+    s = torch.zeros(m, n, device="cuda")
+    for activation, with_residual in itertools.product(ACTIVATIONS, (False, True)):
+        used = residual if with_residual else None
+        out = ops.fp8_gemm(zeros_a, zeros_b, scale_a, scale_b, bias=patterns, activation=activation, residual=used)
+        assert_same_bits(out, rules.store_epilogue(s, patterns, activation, used), f"store {activation} {with_residual}")
+        out = ops.fp8_gated_gemm(zeros_a, zeros_b, zeros_b, scale_a, scale_b, scale_b, bias_gate=patterns,
+                                 bias_up=bias_up, activation=activation, residual=used)
+        assert_same_bits(out, rules.gated_epilogue(s, s, patterns, bias_up, activation, used),
+                         f"gated {activation} {with_residual}")
+
+
+PRACTICAL_SHAPES = ((1, 256, 512), (77, 136, 640), (2 * 37, 264, 256), (300, 576, 384), (64, 128, 4096))
+
+
+@pytest.mark.parametrize("scale_dtype", (torch.float32, E8M0))
+def test_products_meet_the_per_element_bounds(ops, scale_dtype):
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    torch.manual_seed(4)
+    for index, (m, n, k) in enumerate(PRACTICAL_SHAPES):
+        if index % 2 == 1:
+            t = torch.distributions.StudentT(torch.tensor(3.0, device="cuda"))
+            x, w = t.sample((m, k)).bfloat16(), t.sample((n, k)) * k**-0.5
+        else:
+            x = torch.randn(m, k, device="cuda", generator=generator).bfloat16()
+            w = torch.randn(n, k, device="cuda", generator=generator) * k**-0.5
+        if m == 74:
+            x = x.reshape(2, 37, k)
+        w_up = torch.randn(n, k, device="cuda", generator=generator) * k**-0.5
+        a, scale_a = ops.quantize_fp8_rows(x, scale_dtype=scale_dtype)
+        b, scale_b = ops.quantize_fp8_tiles(w, scale_dtype=scale_dtype)
+        up, scale_up = ops.quantize_fp8_tiles(w_up, scale_dtype=scale_dtype)
+        s, error = rules.error_terms(a.cpu(), scale_a.cpu(), b.cpu(), scale_b.cpu())
+        s_up, error_up = rules.error_terms(a.cpu(), scale_a.cpu(), up.cpu(), scale_up.cpu())
+        bias, bias_up = (torch.randn(n, device="cuda", generator=generator).bfloat16() for _ in range(2))
+        residual = (torch.randn(*x.shape[:-1], n, device="cuda", generator=generator) * 4).bfloat16()
+        for activation, with_bias, with_residual in itertools.product(ACTIVATIONS, (False, True), (False, True)):
+            if (ACTIVATIONS.index(activation) + with_bias + 2 * with_residual) % 3:
+                continue
+            options = {"bias": bias if with_bias else None, "residual": residual if with_residual else None}
+            cpu_options = {key: None if value is None else value.cpu() for key, value in options.items()}
+            out = ops.fp8_gemm(a, b, scale_a, scale_b, activation=activation, **options)
+            assert out.shape == (*x.shape[:-1], n)
+            check_bound(out.cpu(), *rules.store_bound(s, error, cpu_options["bias"], activation, cpu_options["residual"]),
+                        f"store {m}x{n}x{k} {activation}")
+            out = ops.fp8_gated_gemm(a, b, up, scale_a, scale_b, scale_up, activation=activation,
+                                     bias_gate=options["bias"], bias_up=bias_up if with_bias else None,
+                                     residual=options["residual"])
+            check_bound(out.cpu(), *rules.gated_bound(s, error, s_up, error_up, cpu_options["bias"],
+                                                      bias_up.cpu() if with_bias else None, activation,
+                                                      cpu_options["residual"]), f"gated {m}x{n}x{k} {activation}")
+
+
+def test_e8m0_scales_give_the_bits_of_fp32_scales(ops):
+    generator = torch.Generator(device="cuda").manual_seed(8)
+    m, n, k = 100, 264, 512
+    a = (torch.randn(m, k, device="cuda", generator=generator) * 30).to(FP8)
+    b, up = ((torch.randn(n, k, device="cuda", generator=generator) * 30).to(FP8) for _ in range(2))
+    tile_rows = -(-n // 128)
+    a_bytes = torch.randint(100, 140, (m, k // 128), device="cuda", generator=generator).to(torch.uint8)
+    a_bytes[3, 1], a_bytes[4, 2], a_bytes[5] = 0, 255, 0
+    b_bytes = torch.randint(110, 130, (tile_rows, k // 128), device="cuda", generator=generator).to(torch.uint8)
+    b_bytes[1, 3] = 255
+    up_bytes = torch.randint(110, 130, (tile_rows, k // 128), device="cuda", generator=generator).to(torch.uint8)
+    one_byte = (column_major(a_bytes.view(E8M0)), b_bytes.view(E8M0), up_bytes.view(E8M0))
+    fp32 = tuple(scale.float() for scale in one_byte)
+    expected = (ops.fp8_gemm(a, b, fp32[0], fp32[1]), ops.fp8_gated_gemm(a, b, up, *fp32))
+    for choice in itertools.product((False, True), repeat=3):
+        scales = [one if use else four for use, one, four in zip(choice, one_byte, fp32)]
+        assert_same_bits(ops.fp8_gemm(a, b, scales[0], scales[1]), expected[0], f"store {choice}")
+        assert_same_bits(ops.fp8_gated_gemm(a, b, up, *scales), expected[1], f"gated {choice}")
+
+
+def gpu_reference(a, scale_a, b, scale_b):
+    """FP32 dequantise-and-matmul on the GPU (no TF32): the full-size stand-in for the CPU oracle."""
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        m, k = a.shape
+        a_deq = a.float() * scale_a.float().reshape(m, k // 128).repeat_interleave(128, 1)
+        b_deq = b.float() * scale_b.float().repeat_interleave(128, 0)[: b.shape[0]].repeat_interleave(128, 1)
+        return a_deq @ b_deq.T
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = previous
+
+
+def test_config3_swiglu_up_projection(ops):
+    """BASELINE config 3 at full size, checked on a 64-row slice by the CPU oracle and in full by the GPU FP32
+    dequantise-and-matmul."""
+    generator = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 512, 4096, generator=generator).bfloat16().cuda()
+    residual = torch.randn(2, 512, 4096, generator=generator).bfloat16().cuda()
+    w_gate = (torch.randn(11008, 4096, generator=generator) / 64).bfloat16().cuda()
+    w_up = (torch.randn(11008, 4096, generator=generator) / 64).bfloat16().cuda()
+    h, _ = ops.fused_add_rms_norm(x, residual, torch.ones(4096, dtype=BF16, device="cuda"), 1e-6)
+    a, scale_a = ops.quantize_fp8_rows(h)
+    gate, scale_gate = ops.quantize_fp8_tiles(w_gate)
+    up, scale_up = ops.quantize_fp8_tiles(w_up)
+    out = ops.fp8_gated_gemm(a, gate, up, scale_a, scale_gate, scale_up)
+    assert out.shape == (2, 512, 11008) and out.dtype == BF16
+    a2 = a.reshape(1024, 4096)
+    s_gate, s_up = gpu_reference(a2, scale_a, gate, scale_gate), gpu_reference(a2, scale_a, up, scale_up)
+    expected = rules.gated_epilogue(s_gate, s_up, None, None, "silu", None)
+    assert max_relative_error(out.reshape(1024, 11008), expected) <= TOLERANCE
+    rows = slice(480, 544)
+    cpu = rules.fp8_gated_gemm(a2[rows].cpu(), gate.cpu(), up.cpu(), scale_a[rows].cpu(), scale_gate.cpu(),
+                               scale_up.cpu(), dtype=torch.float32)
+    assert max_relative_error(out.reshape(1024, 11008)[rows], cpu) <= TOLERANCE
+
+
+def test_config4_down_projection_in_place_and_decode(ops):
+    """BASELINE config 4: M=8192 (residual epilogue written in place) and the M=16 decode shape."""
+    generator = torch.Generator().manual_seed(3)
+    n, k = 4096, 11008
+    w = (torch.randn(n, k, generator=generator) / 105).bfloat16().cuda()
+    b, scale_b = ops.quantize_fp8_tiles(w)
+    for m in (8192, 16):
+        x = (torch.randn(m, k, generator=generator) / 8).bfloat16().cuda()
+        residual = torch.randn(m, n, generator=generator).bfloat16().cuda()
+        a, scale_a = ops.quantize_fp8_rows(x)
+        s = gpu_reference(a, scale_a, b, scale_b)
+        expected = rules.store_epilogue(s, None, "none", residual)
+        buffer = residual.clone()
+        out = ops.fp8_gemm(a, b, scale_a, scale_b, residual=buffer, out=buffer)
+        assert out is buffer
+        assert max_relative_error(out, expected) <= TOLERANCE
+        plain = ops.fp8_gemm(a, b, scale_a, scale_b)
+        assert max_relative_error(plain, s) <= TOLERANCE
+        rows = slice(0, min(m, 32))
+        cpu = rules.fp8_gemm(a[rows].cpu(), b.cpu(), scale_a[rows].cpu(), scale_b.cpu(), residual=residual[rows].cpu(),
+                             dtype=torch.float32)
+        assert max_relative_error(out[rows], cpu) <= TOLERANCE
+        again = ops.fp8_gemm(a, b, scale_a, scale_b)
+        assert_same_bits(again, plain, "same inputs, same bits")
+
+
+def test_layouts_aliases_and_errors(ops):
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    m, n, k = 37, 136, 384
+    a, b, scale_a, scale_b = exact_operands(m, n, k, generator)
+    residual = torch.randn(m, n, device="cuda", generator=generator).bfloat16()
+    expected = ops.fp8_gemm(a, b, scale_a, scale_b, residual=residual)
+    # padded operands, batched a, transposed (row-major) scale_a, 3-D scale_a
+    a_wide = torch.zeros(m, k + 64, device="cuda").to(FP8)
+    a_wide[:, :k] = a
+    b_wide = torch.zeros(n, k + 16, device="cuda").to(FP8)
+    b_wide[:, :k] = b
+    assert_same_bits(ops.fp8_gemm(a_wide[:, :k], b_wide[:, :k], scale_a.contiguous(), scale_b, residual=residual), expected, "padded")
+    # misaligned a (a clone is made)
+    a_off = torch.zeros(m * k + 1, device="cuda").to(FP8)[1:].view(m, k).copy_(a)
+    assert_same_bits(ops.fp8_gemm(a_off, b, scale_a, scale_b, residual=residual), expected, "misaligned")
+    # residual is out
+    buffer = residual.clone()
+    assert ops.fp8_gemm(a, b, scale_a, scale_b, residual=buffer, out=buffer) is buffer
+    assert_same_bits(buffer, expected, "in place")
+    # out overlaps the residual without being the same view: temporary
+    big = torch.zeros(m + 1, n, device="cuda", dtype=BF16)
+    big[:m] = residual
+    shifted = big[1:]
+    ops.fp8_gemm(a, b, scale_a, scale_b, residual=big[:m], out=shifted)
+    assert_same_bits(shifted, expected, "overlapping out")
+    # strided out, stride-0 residual
+    out = torch.zeros(m, 2 * n, device="cuda", dtype=BF16)[:, :n]
+    row = residual[:1].expand(m, n)
+    ops.fp8_gemm(a, b, scale_a, scale_b, residual=row, out=out)
+    assert_same_bits(out.contiguous(), ops.fp8_gemm(a, b, scale_a, scale_b, residual=row.contiguous()), "stride-0 residual")
+    # the halves of one [2f, k] weight
+    both = torch.cat([b, b.flip(0)])
+    scales_both = torch.cat([scale_b, scale_b])[: 2 * (-(-n // 128))]
+    if n % 128 == 0:
+        ops.fp8_gated_gemm(a, both[:n], both[n:], scale_a, scales_both[: n // 128], scales_both[n // 128:])
+    empty = ops.fp8_gemm(a[:0], b, scale_a[:0], scale_b)
+    assert empty.shape == (0, n)
+    with pytest.raises(ValueError, match="match no scaling mode"):
+        ops.fp8_gemm(a, b, scale_a[:, :2], scale_b)
+    with pytest.raises(ValueError, match="activation"):
+        ops.fp8_gemm(a, b, scale_a, scale_b, activation="relu")
+    with pytest.raises(ValueError, match="use_fast_accum"):
+        ops.fp8_gemm(a, b, scale_a, scale_b, use_fast_accum=True)
+    with pytest.raises(ValueError, match="bias must have the shape"):
+        ops.fp8_gemm(a, b, scale_a, scale_b, bias=torch.zeros(n + 8, device="cuda", dtype=BF16))
+    with pytest.raises(ValueError, match="must be on cuda"):
+        ops.fp8_gemm(a, b.cpu(), scale_a, scale_b)
+    with pytest.raises(NotImplementedError):
+        ops.fp8_gemm(a, b, torch.ones(m, 1, device="cuda"), torch.ones(n, 1, device="cuda"))
+
+
+def test_no_wait_ran_out(ops):
+    """Runs last in this file: no device-side wait of the GEMM gave up during the tests above."""
+    from zig_cu_kernels import _lib
+    torch.cuda.synchronize()
+    status = _lib.poll_status(torch.cuda.current_device())
+    assert status.code == 0, f"role {status.code - 1} of block {status.block} gave up at {status.stage}"

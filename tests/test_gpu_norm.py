@@ -1,0 +1,179 @@
+"""fused_add_rms_norm / rms_norm on the GPU: residual stream bit-exact, norm within the reference's bounds
+(3 * 2^-7 relative for BF16 outputs and at most 1 % of elements differing in bits from the PyTorch sequence;
+tests/test_rms_norm.py:52-57, :246-276 of the reference)."""
+
+import pytest
+import torch
+
+from helpers import BF16, FP8, assert_same_bits, from_golden, same_bits
+from oracle import rules
+
+pytestmark = pytest.mark.gpu
+F32 = torch.float32
+EPS = 1e-6
+BF16_BOUND = 3 * 2.0**-7
+FP32_EXACT_BOUND = 2.0**-19
+FP32_PYTORCH_BOUND = 8 * 2.0**-23
+TINY = 2.0**-126
+WIDTHS = [8, 64, 136, 256, 264, 520, 1000, 1032, 4088, 4104, 8200, 16384, 16392, 32768]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import zig_cu_kernels.torch as z
+    return z
+
+
+def within(tensor, reference, relative, name):
+    error = (tensor.double() - reference.double()).abs()
+    allowed = relative * reference.double().abs() + TINY
+    assert bool((error <= allowed).all()), f"{name}: max excess {float((error - allowed).max())}"
+
+
+def test_golden_rows(ops, golden):
+    g = golden["norm"]
+    differing, total = 0, 0
+    for index in range(int(g["norm_cases"])):
+        x, other = from_golden(g[f"norm{index}_x"], BF16).cuda(), from_golden(g[f"norm{index}_other"], BF16).cuda()
+        w_bf16 = from_golden(g[f"norm{index}_w_bf16"], BF16).cuda()
+        w_f32 = from_golden(g[f"norm{index}_w_f32"], F32).cuda()
+        y, h = ops.fused_add_rms_norm(x, other, w_bf16, EPS)
+        assert_same_bits(h, from_golden(g[f"norm{index}_h"], BF16), "residual_out")
+        for weight, zc, key in ((w_bf16, False, "y_bf16"), (None, False, "y_none"), (w_f32, False, "y_f32"),
+                                (w_bf16, True, "y_zc")):
+            y, _ = ops.fused_add_rms_norm(x, other, weight, EPS, zero_centered=zc)
+            expected = from_golden(g[f"norm{index}_{key}"], BF16)
+            within(y.cpu(), expected, BF16_BOUND, key)
+            differing += int((~same_bits(y.cpu(), expected)).sum())
+            total += y.numel()
+    assert differing <= 0.01 * total, f"{differing} of {total} BF16 results differ in bits"
+
+
+NORMS = [
+    (BF16, None, False, BF16, False), (BF16, BF16, False, BF16, False), (BF16, F32, False, BF16, False),
+    (BF16, BF16, True, BF16, False), (BF16, F32, True, BF16, False), (F32, None, False, F32, False),
+    (F32, F32, False, F32, False), (F32, BF16, False, BF16, False), (F32, BF16, False, F32, False),
+    (F32, F32, True, F32, False), (BF16, None, False, BF16, True), (BF16, BF16, False, BF16, True),
+    (BF16, BF16, True, BF16, True), (F32, BF16, False, BF16, True), (F32, BF16, False, F32, True),
+]
+
+
+@pytest.mark.parametrize("dtype,weight_dtype,zero_centered,out_dtype,residual", NORMS)
+def test_norms_meet_the_bounds_of_their_regime(ops, dtype, weight_dtype, zero_centered, out_dtype, residual):
+    torch.manual_seed(0)
+    differing, total = 0, 0
+    for width in WIDTHS:
+        weight = None if weight_dtype is None else (torch.randn(width, device="cuda") * 0.5 + 1).to(weight_dtype)
+        for rows in (1, 13):
+            x = (torch.randn(rows, width, device="cuda") * 2).to(dtype)
+            if rows > 1:
+                x[rows // 2] = 0
+            if residual:
+                other = (torch.randn(rows, width, device="cuda") * 2).to(dtype)
+                y, h = ops.fused_add_rms_norm(x, other, weight, EPS, zero_centered=zero_centered, out_dtype=out_dtype)
+                assert_same_bits(h, x + other, f"residual_out {width} {rows}")
+                again = ops.rms_norm(h, weight, EPS, zero_centered=zero_centered, out_dtype=out_dtype)
+                assert_same_bits(y, again, f"y against the norm of residual_out {width} {rows}")
+            else:
+                h = x
+                y = ops.rms_norm(x, weight, EPS, zero_centered=zero_centered, out_dtype=out_dtype)
+            assert (y.shape, y.dtype) == (x.shape, out_dtype)
+            pytorch = rules.rms_norm(h, weight, zero_centered, EPS, out_dtype)
+            if out_dtype == BF16:
+                within(y, pytorch, BF16_BOUND, f"y against PyTorch {width} {rows}")
+                differing += int((~same_bits(y, pytorch)).sum())
+                total += y.numel()
+            else:
+                within(y, rules.rms_norm_exact(h, weight, zero_centered, EPS), FP32_EXACT_BOUND, f"y vs FP64 {width}")
+                within(y, pytorch, FP32_PYTORCH_BOUND, f"y vs PyTorch {width}")
+    if out_dtype == BF16:
+        assert differing <= 0.01 * total, f"{differing} of {total} differ"
+
+
+def test_config3_norm(ops):
+    """BASELINE config 3 front end: x, residual (2, 512, 4096) BF16 seed 2, weight ones, eps 1e-6."""
+    generator = torch.Generator().manual_seed(2)
+    x = torch.randn(2, 512, 4096, generator=generator).bfloat16().cuda()
+    residual = torch.randn(2, 512, 4096, generator=generator).bfloat16().cuda()
+    weight = torch.ones(4096, dtype=BF16, device="cuda")
+    y, h = ops.fused_add_rms_norm(x, residual, weight, EPS)
+    expected_y, expected_h = rules.fused_add_rms_norm(x.cpu(), residual.cpu(), weight.cpu(), EPS)
+    assert_same_bits(h, expected_h, "h")
+    within(y.cpu(), expected_y, BF16_BOUND, "y")
+    assert float((~same_bits(y.cpu(), expected_y)).float().mean()) <= 0.01
+    relative = (y.cpu().double() - expected_y.double()).abs().max() / expected_y.double().abs().max()
+    assert relative <= 1e-2
+
+
+def test_exact_aliases_run_in_place_and_overlaps_go_through_temporaries(ops):
+    torch.manual_seed(3)
+    x = torch.randn(13, 1032, device="cuda", dtype=BF16)
+    other = torch.randn(13, 1032, device="cuda", dtype=BF16)
+    weight = torch.randn(1032, device="cuda", dtype=BF16)
+    y, h = ops.fused_add_rms_norm(x, other, weight, EPS)
+    for out_is, h_is in (("x", "other"), ("other", "x"), ("new", "x"), ("x", "new")):
+        xs, os_ = x.clone(), other.clone()
+        pick = {"x": xs, "other": os_}
+        out = pick.get(out_is, torch.empty_like(x))
+        h_out = pick.get(h_is, torch.empty_like(x))
+        got_y, got_h = ops.fused_add_rms_norm(xs, os_, weight, EPS, out=out, residual_out=h_out)
+        assert got_y is out and got_h is h_out
+        assert_same_bits(out, y, f"y in {out_is}")
+        assert_same_bits(h_out, h, f"h in {h_is}")
+    # outputs that overlap an input without being the same view
+    buffer = torch.empty(14 * 1032, device="cuda", dtype=BF16)
+    xs = buffer[:13 * 1032].view(13, 1032).copy_(x)
+    shifted = buffer[1032:].view(13, 1032)
+    got_y, got_h = ops.fused_add_rms_norm(xs, other, weight, EPS, out=shifted)
+    assert_same_bits(got_y, y, "overlapping out")
+    # strided and misaligned inputs and outputs
+    wide = torch.randn(13, 2 * 1032 + 8, device="cuda", dtype=BF16)
+    xs, os_ = wide[:, 1:1033], wide[:, 1040:2072]
+    ey, eh = ops.fused_add_rms_norm(xs.contiguous(), os_.contiguous(), weight, EPS)
+    out = torch.empty(13, 2064, device="cuda", dtype=BF16)[:, ::2]
+    got_y, got_h = ops.fused_add_rms_norm(xs, os_, weight, EPS, out=out)
+    assert_same_bits(got_y.contiguous(), ey, "strided y")
+    assert_same_bits(got_h, eh, "strided h")
+    with pytest.raises(ValueError, match="share memory"):
+        ops.fused_add_rms_norm(x, other, weight, EPS, out=x, residual_out=x)
+
+
+def test_rows_do_not_depend_on_the_batch(ops):
+    torch.manual_seed(4)
+    x = torch.randn(257, 4096, device="cuda", dtype=BF16)
+    other = torch.randn(257, 4096, device="cuda", dtype=BF16)
+    weight = torch.randn(4096, device="cuda", dtype=BF16)
+    y, h = ops.fused_add_rms_norm(x, other, weight, EPS)
+    for rows in (1, 5, 64):
+        y_part, h_part = ops.fused_add_rms_norm(x[100:100 + rows], other[100:100 + rows], weight, EPS)
+        assert_same_bits(y_part, y[100:100 + rows], f"{rows} rows")
+        assert_same_bits(h_part, h[100:100 + rows], f"{rows} rows")
+
+
+def test_fp8_output_with_a_given_scale(ops):
+    torch.manual_seed(5)
+    x = torch.randn(13, 1032, device="cuda", dtype=BF16) * 3
+    weight = torch.randn(1032, device="cuda", dtype=BF16)
+    scale = torch.tensor(0.0371, device="cuda")
+    y = ops.rms_norm(x, weight, EPS)
+    q = ops.rms_norm_op(x, weight, scale, EPS, False, FP8)
+    expected = (y.float() / scale).clamp(-448, 448).to(FP8)
+    assert_same_bits(q, expected, "codes of the BF16 norm")
+
+
+def test_empty_inputs_and_errors(ops):
+    weight = torch.ones(64, device="cuda", dtype=BF16)
+    y, h = ops.fused_add_rms_norm(torch.empty(0, 64, device="cuda", dtype=BF16),
+                                  torch.empty(0, 64, device="cuda", dtype=BF16), weight, EPS)
+    assert y.shape == (0, 64) and h.shape == (0, 64)
+    x = torch.ones(2, 64, device="cuda", dtype=BF16)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        ops.rms_norm(torch.ones(2, 12, device="cuda", dtype=BF16), None, EPS)
+    with pytest.raises(ValueError, match="residual must have the shape"):
+        ops.fused_add_rms_norm(x, x[:, :32], weight, EPS)
+    with pytest.raises(ValueError, match="zero_centered needs a weight"):
+        ops.rms_norm(x, None, EPS, zero_centered=True)
+    with pytest.raises(TypeError, match="eps must be a Python number"):
+        ops.rms_norm(x, None, torch.tensor(1e-6))
+    with pytest.raises(OverflowError):
+        ops.rms_norm(x, None, 1e39)

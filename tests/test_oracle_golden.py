@@ -1,0 +1,118 @@
+"""The CPU oracle against the golden vectors that the reference's own Python code produced (tests/golden)."""
+
+import torch
+
+from helpers import BF16, E8M0, FP8, assert_same_bits, from_golden
+from oracle import rules
+
+SCALES = {"f32": torch.float32, "e8m0": E8M0}
+INPUTS = {"f32": torch.float32, "bf16": BF16}
+
+
+def test_row_quantizer_rules_match_the_reference(golden):
+    g = golden["quantizers"]
+    for tag, dtype in INPUTS.items():
+        x = from_golden(g[f"rows_x_{tag}"], dtype)
+        for stag, scale_dtype in SCALES.items():
+            codes, scales = rules.quantize_rows(x, scale_dtype)
+            assert_same_bits(scales, from_golden(g[f"rows_scales_{tag}_{stag}"], scale_dtype), f"scales {tag} {stag}")
+            assert_same_bits(codes, from_golden(g[f"rows_codes_{tag}_{stag}"], FP8), f"codes {tag} {stag}")
+
+
+def test_tile_quantizer_rules_match_the_reference(golden):
+    g = golden["quantizers"]
+    for n in (136, 200):
+        for tag, dtype in INPUTS.items():
+            w = from_golden(g[f"tiles{n}_w_{tag}"], dtype)
+            for stag, scale_dtype in SCALES.items():
+                codes, scales = rules.quantize_tiles(w, scale_dtype)
+                assert_same_bits(scales, from_golden(g[f"tiles{n}_scales_{tag}_{stag}"], scale_dtype), f"{n} {tag} {stag}")
+                assert_same_bits(codes, from_golden(g[f"tiles{n}_codes_{tag}_{stag}"], FP8), f"{n} {tag} {stag}")
+
+
+def test_e8m0_bytes_agree_with_frexp_on_every_exponent():
+    """The integer form of the E8M0 rule equals the frexp form of the reference for powers of two and neighbours."""
+    values = []
+    for exponent in range(-149, 128):
+        base = torch.tensor(2.0 ** exponent, dtype=torch.float32)
+        values += [base, torch.nextafter(base, torch.tensor(float("inf"))), torch.nextafter(base, torch.tensor(0.0))]
+    t = torch.stack(values + [torch.tensor(0.0), torch.tensor(float("inf")), torch.tensor(float("nan"))])
+    mantissa, exponent = torch.frexp(t)
+    byte = (exponent - (mantissa == 0.5).to(exponent.dtype) + 127).clamp(0, 254)
+    byte = torch.where(t == 0, 127, byte)
+    byte = torch.where(t.isnan() | t.isinf(), 255, byte)
+    assert torch.equal(rules.e8m0_byte_of(t), byte.to(torch.uint8))
+    decoded = rules.e8m0_decode(torch.arange(256, dtype=torch.uint8))
+    assert_same_bits(decoded, torch.arange(256, dtype=torch.uint8).view(E8M0).float(), "decode")
+
+
+def config1_inputs():
+    generator = torch.Generator().manual_seed(0)
+    a = torch.randn(256, 1024, generator=generator).bfloat16()
+    b = (torch.randn(512, 1024, generator=generator) / 32).bfloat16()
+    return a, b
+
+
+def test_config1_product_matches_the_reference(golden):
+    g = golden["gemm"]
+    a_hp, b_hp = config1_inputs()
+    a, scale_a = rules.quantize_rows(a_hp)
+    b, scale_b = rules.quantize_tiles(b_hp)
+    assert_same_bits(a, from_golden(g["c1_a"], FP8), "a codes")
+    assert_same_bits(b, from_golden(g["c1_b"], FP8), "b codes")
+    assert_same_bits(scale_a, from_golden(g["c1_scale_a"], torch.float32), "scale_a")
+    assert_same_bits(scale_b, from_golden(g["c1_scale_b"], torch.float32), "scale_b")
+    assert_same_bits(rules.fp8_gemm(a, b, scale_a, scale_b, dtype=torch.float64),
+                     from_golden(g["c1_out_fp64_path"], BF16), "fp64 path")
+    assert_same_bits(rules.fp8_gemm(a, b, scale_a, scale_b, dtype=torch.float32),
+                     from_golden(g["c1_out_fp32_path"], BF16), "fp32 path")
+
+
+def test_epilogue_rounding_points_match_the_reference(golden):
+    g = golden["gemm"]
+    t = {name: from_golden(g[f"ep_{name}"], dtype) for name, dtype in (
+        ("a", FP8), ("b", FP8), ("up", FP8), ("scale_a", torch.float32), ("scale_b", torch.float32),
+        ("scale_up", torch.float32), ("bias", BF16), ("bias_up", BF16), ("residual", BF16), ("s", torch.float32),
+        ("s_up", torch.float32))}
+    s = rules.block_sums(t["a"], t["scale_a"], t["b"], t["scale_b"]).float()
+    s_up = rules.block_sums(t["a"], t["scale_a"], t["up"], t["scale_up"]).float()
+    assert_same_bits(s, t["s"], "exact sums")
+    assert_same_bits(s_up, t["s_up"], "exact up sums")
+    assert_same_bits(rules.store_epilogue(s, t["bias"], "none", t["residual"]), from_golden(g["ep_store_none"], BF16), "store")
+    assert_same_bits(rules.store_epilogue(s, None, "none", None), from_golden(g["ep_store_none_plain"], BF16), "plain")
+    assert_same_bits(rules.gated_epilogue(s, s_up, t["bias"], t["bias_up"], "none", t["residual"]),
+                     from_golden(g["ep_gated_none"], BF16), "gated")
+    assert_same_bits(rules.store_epilogue(s, t["bias"], "silu", t["residual"]), from_golden(g["ep_store_silu_cpu"], BF16), "silu")
+    assert_same_bits(rules.gated_epilogue(s, s_up, None, t["bias_up"], "silu", None),
+                     from_golden(g["ep_gated_silu_cpu"], BF16), "gated silu")
+
+
+def test_norm_rules_match_the_reference(golden):
+    g = golden["norm"]
+    for index in range(int(g["norm_cases"])):
+        x, other = from_golden(g[f"norm{index}_x"], BF16), from_golden(g[f"norm{index}_other"], BF16)
+        w_bf16, w_f32 = from_golden(g[f"norm{index}_w_bf16"], BF16), from_golden(g[f"norm{index}_w_f32"], torch.float32)
+        y, h = rules.fused_add_rms_norm(x, other, w_bf16)
+        assert_same_bits(h, from_golden(g[f"norm{index}_h"], BF16), "h")
+        assert_same_bits(y, from_golden(g[f"norm{index}_y_bf16"], BF16), "y bf16 weight")
+        assert_same_bits(rules.rms_norm(h, None), from_golden(g[f"norm{index}_y_none"], BF16), "y no weight")
+        assert_same_bits(rules.rms_norm(h, w_f32), from_golden(g[f"norm{index}_y_f32"], BF16), "y f32 weight")
+        assert_same_bits(rules.rms_norm(h, w_bf16, zero_centered=True), from_golden(g[f"norm{index}_y_zc"], BF16), "y zc")
+        key = f"norm{index}_exact_bf16"
+        if key in g:
+            assert torch.equal(rules.rms_norm_exact(h, w_bf16), from_golden(g[key], torch.float64))
+
+
+def test_sharded_mlp_partials_sum_to_the_unsharded_mlp():
+    """Oracle-level statement of the tensor-parallel split: gate/up by columns, down by K, partials summed."""
+    generator = torch.Generator().manual_seed(4)
+    m, hidden, inter = 16, 256, 512
+    tokens = torch.randn(m, hidden, generator=generator).bfloat16()
+    w_gate = (torch.randn(inter, hidden, generator=generator) / 16).bfloat16()
+    w_up = (torch.randn(inter, hidden, generator=generator) / 16).bfloat16()
+    w_down = (torch.randn(hidden, inter, generator=generator) / 22).bfloat16()
+    whole = rules.mlp(tokens, w_gate, w_up, w_down).float()
+    for world in (2, 4):
+        total = sum(rules.mlp_shard(tokens, w_gate, w_up, w_down, rank, world).float() for rank in range(world))
+        error = (total - whole).abs().max() / whole.abs().max()
+        assert error < 1e-2, (world, float(error))

@@ -30,6 +30,12 @@ constexpr int kATile = kBM * kBK, kBTile = kBN * kBK, kStageBytes = kATile + kBT
 constexpr int kBoxRows = 64;  // rows of one B box
 constexpr int kThreads = 384, kEpilogueThreads = 256;  // three warpgroups: two epilogue, one for the copy and MMA warps
 constexpr int kProducerWarp = 8, kMmaWarp = 9;
+// Register redistribution. The block starts at kLaunchRegs per thread (what ptxas grants 384 threads); the third
+// warpgroup drops to kIdleRegs and the two epilogue warpgroups rise to kEpilogueRegs. The rise BLOCKS until the
+// block's own pool holds enough released registers, so released must cover taken exactly or the kernel hangs.
+constexpr int kLaunchRegs = 168, kIdleRegs = 40, kEpilogueRegs = 232;
+static_assert((kLaunchRegs - kIdleRegs) * 128 >= (kEpilogueRegs - kLaunchRegs) * kEpilogueThreads,
+              "the epilogue warpgroups would wait forever for registers");
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kBand = 8;  // M tiles that share a band of the tile walk
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -237,7 +243,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = sh->tmem_base;
 
     if (warp >= 8) {
-      ptx::reg_release<48>();
+      ptx::reg_release<kIdleRegs>();
       if (warp == kProducerWarp) {
         if (lane == 0) {
             uint32_t it = 0;
@@ -304,7 +310,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         __syncwarp();
       }
     } else {
-        ptx::reg_take<232>();
+        ptx::reg_take<kEpilogueRegs>();
         const uint32_t group = warp / 4, quarter = warp % 4;
         const uint32_t lane_row = quarter * 32 + lane;
         const bool sa_e8m0 = p.e8m0_bits & 1u, sb_e8m0 = p.e8m0_bits & 2u, su_e8m0 = p.e8m0_bits & 4u;
