@@ -1,0 +1,96 @@
+"""Tensor-parallel SwiGLU MLP on the block-scaled FP8 ops (new work; the reference has no multi-GPU code).
+
+Sharding (one process per GPU, `torch.distributed` with NCCL over NVLink/NVSwitch):
+  * `w_gate`, `w_up` `[I, H]` are split by rows (output columns of the up projection) into `I/g` per rank;
+  * `w_down` `[H, I]` is split along K into `I/g` per rank;
+  * every rank holds all tokens; `fp8_gated_gemm` -> `quantize_fp8_rows` -> `fp8_gemm` give a BF16 partial `(M, H)`;
+  * the partials are summed with one exchange: all-reduce, or reduce-scatter over token rows.
+`I/g` is a multiple of 128, so no scale group or weight tile straddles a shard and each shard's codes and scales are
+slices of the unsharded ones, bit for bit. Tokens are processed in row chunks so that the exchange of chunk c runs on
+a side stream under the GEMMs of chunk c+1.
+"""
+
+import torch
+
+from . import torch as ops
+
+GROUP = 128
+
+
+def shard_bounds(inter, rank, world):
+    if inter % (world * GROUP):
+        raise ValueError(f"the intermediate size {inter} must be a multiple of {world} * {GROUP}")
+    step = inter // world
+    return rank * step, (rank + 1) * step
+
+
+class TensorParallelMLP:
+    """Holds this rank's quantized weight shards and runs the forward pass of its share."""
+
+    def __init__(self, w_gate, w_up, w_down, rank=0, world=1, group=None, scale_dtype=torch.float32, chunks=1,
+                 exchange="all_reduce"):
+        if exchange not in ("all_reduce", "reduce_scatter"):
+            raise ValueError("exchange must be all_reduce or reduce_scatter")
+        inter, hidden = w_gate.shape
+        if tuple(w_up.shape) != (inter, hidden) or tuple(w_down.shape) != (hidden, inter):
+            raise ValueError("w_gate and w_up must be [I, H] and w_down [H, I]")
+        self.rank, self.world, self.group, self.chunks, self.exchange = rank, world, group, chunks, exchange
+        self.hidden, self.inter = hidden, inter
+        self.scale_dtype = scale_dtype
+        lo, hi = shard_bounds(inter, rank, world)
+        self.gate, self.scale_gate = ops.quantize_fp8_tiles(w_gate[lo:hi], scale_dtype=scale_dtype)
+        self.up, self.scale_up = ops.quantize_fp8_tiles(w_up[lo:hi], scale_dtype=scale_dtype)
+        self.down, self.scale_down = ops.quantize_fp8_tiles(w_down[:, lo:hi], scale_dtype=scale_dtype)
+        self.comm_stream = torch.cuda.Stream() if world > 1 else None
+        self.launches = 0
+        self.kernel_events = None  # set to {} to collect (start, end) CUDA events per kernel name
+
+    def _run(self, name, function, *arguments, **keywords):
+        self.launches += 1
+        if self.kernel_events is None:
+            return function(*arguments, **keywords)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        result = function(*arguments, **keywords)
+        end.record()
+        self.kernel_events.setdefault(name, []).append((start, end))
+        return result
+
+    def partial(self, tokens, out=None):
+        """BF16 partial `(m, H)` of this rank for `tokens (m, H)`: four kernels."""
+        a, scale_a = self._run("quantize_tokens", ops.quantize_fp8_rows, tokens, scale_dtype=self.scale_dtype)
+        act = self._run("gated_gemm", ops.fp8_gated_gemm, a, self.gate, self.up, scale_a, self.scale_gate,
+                        self.scale_up)
+        q, scale_q = self._run("quantize_act", ops.quantize_fp8_rows, act, scale_dtype=self.scale_dtype)
+        return self._run("down_gemm", ops.fp8_gemm, q, self.down, scale_q, self.scale_down, out=out)
+
+    def forward(self, tokens):
+        """`(m, H)` BF16 result: the full sum on every rank (all_reduce) or this rank's `m/world` rows
+        (reduce_scatter). With one rank this is the plain MLP."""
+        import torch.distributed as dist
+
+        m = tokens.shape[0]
+        if self.world == 1:
+            return self.partial(tokens)
+        chunks = max(1, min(self.chunks, m // (self.world * GROUP) or 1))
+        bounds = [m * c // chunks for c in range(chunks + 1)]
+        scatter = self.exchange == "reduce_scatter"
+        if scatter and any((hi - lo) % self.world for lo, hi in zip(bounds, bounds[1:])):
+            raise ValueError("reduce_scatter needs chunk row counts that are multiples of the world size")
+        partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=tokens.device)
+        result = torch.empty(m // self.world, self.hidden, dtype=torch.bfloat16, device=tokens.device) if scatter \
+            else partial
+        compute = torch.cuda.current_stream()
+        offset = 0
+        for lo, hi in zip(bounds, bounds[1:]):
+            self.partial(tokens[lo:hi], out=partial[lo:hi])
+            self.comm_stream.wait_stream(compute)
+            with torch.cuda.stream(self.comm_stream):
+                if scatter:
+                    rows = (hi - lo) // self.world
+                    dist.reduce_scatter_tensor(result[offset:offset + rows], partial[lo:hi], group=self.group)
+                    offset += rows
+                else:
+                    dist.all_reduce(partial[lo:hi], group=self.group)
+        compute.wait_stream(self.comm_stream)
+        return result
