@@ -116,6 +116,23 @@ int zck_fp8_gated_gemm(const void* a, const void* w_gate, const void* w_up, cons
                        const void* bias_up, const void* residual, void* ws_parts, void* ws_counters,
                        const ZckGemmSizes* sizes, int device, void* stream);
 
+/* No counterpart in the reference (its launchers always get their workspace from the caller's allocator).
+ * zck_fp8_gemm for a host that must not allocate device memory: a program that calls this ABI straight from a
+ * serving loop, with no caching allocator behind it. Such a host has typically given all free HBM to its own arena at
+ * start-up, so a later cudaMalloc may fail, and a successful one still serialises the device in the middle of a
+ * decode step. Here the split-K scratch (partial tiles, tile counters, wait-limit record) is a device array inside the
+ * library: 19 MiB + 4.25 KiB, held by every GPU that loads the library until the process exits. It fits 152 partial
+ * tiles and 1024 counters, which covers every split plan on a 148-SM part; a product that would need more returns
+ * ZCK_ERR_ARGUMENT and a message that points to zck_fp8_gemm. `sizes->splits` > 1 requests that many K splits,
+ * anything else lets the library plan. The call itself allocates nothing (no cudaMalloc/cudaFree, no library that
+ * allocates) and needs neither zck_init nor zck_gemm_plan.
+ * The FIRST call on a device looks up the array's device address and raises the kernel's shared-memory limit; make
+ * that call before any CUDA stream capture begins. All calls share the one array, which keeps the previous call's
+ * contents: the counters and the record are cleared on `stream` before each launch, and two calls whose kernels
+ * could run at the same time (different streams) race on it: do not overlap them. */
+int zck_fp8_gemm_static(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out,
+                        const void* bias, const void* residual, const ZckGemmSizes* sizes, int device, void* stream);
+
 /* Device-side wait limits never trap: a role whose wait runs out records where it gave up and the block exits.
  * `zck_poll_status` reads that record from host-mapped memory without synchronizing.
  * (The reference traps after 1 s instead: zig/mm_sm100.zig:58-64.) */

@@ -1,0 +1,99 @@
+"""`zck_fp8_gemm_static`: the FP8 GEMM for hosts that cannot allocate device memory.
+
+Some users of the C ABI are not PyTorch programs: a serving loop that has already given every free byte of HBM to its
+own arena cannot count on cudaMalloc succeeding, and cannot afford the device-wide stall of one in the middle of a
+decode step. For them the library carries the split-K scratch itself. This test drives the entry point through ctypes
+(as such a host would) and checks that it produces exactly what `zck_fp8_gemm` produces with a caller-provided
+workspace, twice in a row on different data, because the second call finds the first call's leftovers in the
+shared scratch.
+The file name sorts last so that a run that stops at the first failure has already run every other test.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+from helpers import BF16, FP8, assert_same_bits
+from zig_cu_kernels import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def operands(m, n, k, seed):
+    generator = torch.Generator(device="cuda").manual_seed(seed)
+    a = (torch.randn(m, k, device="cuda", generator=generator) * 40).to(FP8)
+    b = (torch.randn(n, k, device="cuda", generator=generator) * 40).to(FP8)
+    scale_a = (torch.rand(k // 128, m, device="cuda", generator=generator) + 0.5).t()
+    scale_b = torch.rand(-(-n // 128), k // 128, device="cuda", generator=generator) + 0.5
+    bias = torch.randn(n, device="cuda", generator=generator).bfloat16()
+    residual = torch.randn(m, n, device="cuda", generator=generator).bfloat16()
+    return a, b, scale_a, scale_b, bias, residual
+
+
+def sizes_for(a, b, scale_a, scale_b, out, residual, splits=1):
+    m, k = a.shape
+    return _lib.GemmSizes(a_stride=a.stride(0), b_stride=b.stride(0), sa_row=scale_a.stride(0), sa_blk=scale_a.stride(1),
+                          sb_row=scale_b.stride(0), sb_blk=scale_b.stride(1), su_row=0, su_blk=0,
+                          out_stride=out.stride(0), residual_stride=residual.stride(0), m=m, n=b.shape[0], k=k,
+                          e8m0_bits=0, activation=_lib.ACTIVATIONS["silu"], splits=splits)
+
+
+def with_caller_workspace(lib, device, stream, tensors):
+    a, b, scale_a, scale_b, bias, residual = tensors
+    out = torch.empty(a.shape[0], b.shape[0], device="cuda", dtype=BF16)
+    sizes = sizes_for(a, b, scale_a, scale_b, out, residual)
+    part_bytes, counters = ctypes.c_size_t(), ctypes.c_uint32()
+    _lib.check(lib.zck_gemm_plan(ctypes.byref(sizes), 0, device, ctypes.byref(part_bytes), ctypes.byref(counters)))
+    parts = torch.empty(max(part_bytes.value, 16), dtype=torch.uint8, device="cuda")
+    tile_counters = torch.zeros(max(counters.value, 1), dtype=torch.int32, device="cuda")
+    _lib.check(lib.zck_fp8_gemm(a.data_ptr(), b.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), out.data_ptr(),
+                                bias.data_ptr(), residual.data_ptr(), parts.data_ptr(), tile_counters.data_ptr(),
+                                ctypes.byref(sizes), device, stream))
+    return out, sizes.splits
+
+
+def with_static_scratch(lib, device, stream, tensors, out):
+    a, b, scale_a, scale_b, bias, residual = tensors
+    sizes = sizes_for(a, b, scale_a, scale_b, out, residual)
+    _lib.check(lib.zck_fp8_gemm_static(a.data_ptr(), b.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                       out.data_ptr(), bias.data_ptr(), residual.data_ptr(), ctypes.byref(sizes),
+                                       device, stream))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 2048), (300, 520, 512)])
+def test_static_scratch_gemm_equals_the_workspace_gemm_twice_in_a_row(m, n, k):
+    lib = _lib.library()
+    device = torch.cuda.current_device()
+    stream = torch.cuda.current_stream().cuda_stream
+    first, second = operands(m, n, k, 21), operands(m, n, k, 22)
+    expected_first, splits = with_caller_workspace(lib, device, stream, first)
+    expected_second, _ = with_caller_workspace(lib, device, stream, second)
+    if (m, n, k) == (16, 4096, 2048):
+        assert splits > 1, "this shape is meant to exercise the split-K scratch"
+    # outputs exist before the calls under test: between here and the comparison nothing allocates device memory
+    out_first = torch.empty(m, n, device="cuda", dtype=BF16)
+    out_second = torch.empty(m, n, device="cuda", dtype=BF16)
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    with_static_scratch(lib, device, stream, first, out_first)
+    with_static_scratch(lib, device, stream, second, out_second)
+    assert torch.cuda.memory_stats()["allocation.all.allocated"] == before
+    torch.cuda.synchronize()
+    assert_same_bits(out_first, expected_first, "first call")
+    assert_same_bits(out_second, expected_second, "second call (scratch reused)")
+
+
+def test_static_scratch_rejects_what_does_not_fit():
+    lib = _lib.library()
+    device = torch.cuda.current_device()
+    stream = torch.cuda.current_stream().cuda_stream
+    tensors = operands(16, 8192, 4096, 23)  # 32 tiles; 8 requested splits would need 256 partial tiles
+    a, b, scale_a, scale_b, bias, residual = tensors
+    out = torch.empty(16, 8192, device="cuda", dtype=BF16)
+    sizes = sizes_for(a, b, scale_a, scale_b, out, residual, splits=8)
+    code = lib.zck_fp8_gemm_static(a.data_ptr(), b.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), out.data_ptr(),
+                                   bias.data_ptr(), residual.data_ptr(), ctypes.byref(sizes), device, stream)
+    assert code == -1
+    message = lib.zck_last_error().decode()
+    assert "static scratch" in message and "zck_fp8_gemm" in message

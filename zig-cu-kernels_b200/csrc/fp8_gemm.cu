@@ -612,3 +612,143 @@ extern "C" int zck_fp8_gated_gemm(const void* a, const void* w_gate, const void*
     return launch_gemm(true, a, w_gate, w_up, scale_a, scale_gate, scale_up, out, bias_gate, bias_up, residual, ws_parts,
                        ws_counters, sizes, device, stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// zck_fp8_gemm_static: the plain FP8 GEMM for hosts that must not allocate device memory.
+//
+// Who needs it: a program that drives this ABI directly from a serving loop, without a caching allocator behind it.
+// Such a host has usually handed all free HBM to its own arena (KV cache, activations) at start-up, so a later
+// cudaMalloc can fail, and even when it succeeds it serialises the whole device, which a decode step that is a few
+// microseconds long cannot afford. zck_fp8_gemm makes that caller provide the split-K workspace; this variant brings
+// its own: the partial tiles, the tile counters and the wait-limit record live in one file-scope device array.
+//
+// The array is part of the library image: every GPU that loads the library carries its kStaticScratchBytes until
+// the process exits. All calls share it and it keeps what the last call left, so the counters and the record are
+// cleared on the stream before each launch; two calls whose kernels overlap on the GPU (different streams, or
+// concurrent graph branches) race on it and must not be made.
+// ---------------------------------------------------------------------------------------------------------------
+namespace zck {
+
+constexpr uint32_t kStaticUnits = 152;  // partial tiles: every plan of a 148-SM part fits (units <= SMs when split)
+constexpr size_t kStaticPartBytes = (size_t)kStaticUnits * kTileFloats * sizeof(float);  // 19 MiB
+constexpr uint32_t kStaticCounters = 1024;
+constexpr size_t kStaticCounterOffset = kStaticPartBytes;
+constexpr size_t kStaticStatusOffset = kStaticCounterOffset + kStaticCounters * sizeof(uint32_t);
+constexpr size_t kStaticScratchBytes = kStaticStatusOffset + 256;
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticState {
+    bool ready = false;
+    unsigned char* base = nullptr;  // device address of g_static_scratch on this device
+    int sm_count = 0;
+};
+static StaticState g_static_state[kMaxDevices];
+static std::mutex g_static_lock;
+
+// Once per device, with that device current. In host code `g_static_scratch` is only a handle for the runtime, not
+// an address a kernel could use; cudaGetSymbolAddress turns it into this device's address.
+static int static_setup(int device, StaticState** out) {
+    if (device < 0 || device >= kMaxDevices) return fail(ZCK_ERR_ARGUMENT, "device %d is out of range", device);
+    std::lock_guard<std::mutex> lock(g_static_lock);
+    StaticState* state = &g_static_state[device];
+    *out = state;
+    if (state->ready) return ZCK_OK;
+    int major = 0, sms = 0;
+    ZCK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    if (major != 10) return fail(ZCK_ERR_UNSUPPORTED, "device %d is not an sm_100 device", device);
+    ZCK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    void* address = nullptr;
+    ZCK_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
+    if (!g_encode) {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult query;
+        cudaError_t error = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query);
+        if (error != cudaSuccess || query != cudaDriverEntryPointSuccess || !entry)
+            return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        g_encode = reinterpret_cast<EncodeTiled>(entry);
+    }
+    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    state->base = static_cast<unsigned char*>(address);
+    state->sm_count = sms;
+    state->ready = true;
+    return ZCK_OK;
+}
+
+// Same tensor map as tensor_map_of, encoded on the spot (no host-side cache, so nothing here grows).
+static int encode_map(const void* base, uint64_t rows, uint64_t k, uint64_t stride, uint32_t box_rows, CUtensorMap* out) {
+    cuuint64_t dims[2] = {k, rows};
+    cuuint64_t strides[1] = {rows > 1 ? stride : k};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult result = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                               element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (result != CUDA_SUCCESS) return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", (int)result);
+    return ZCK_OK;
+}
+
+}  // namespace zck
+
+extern "C" int zck_fp8_gemm_static(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out,
+                                   const void* bias, const void* residual, const ZckGemmSizes* s, int device,
+                                   void* stream) {
+    int code = check_sizes(s);
+    if (code != ZCK_OK) return code;
+    if (s->m == 0 || s->n == 0) return ZCK_OK;
+    ZCK_REQUIRE(a && b && scale_a && scale_b && out, "an operand pointer is NULL");
+    ZCK_REQUIRE(aligned(a, 16) && aligned(b, 16), "a and b must start at a multiple of 16 bytes");
+    ZCK_REQUIRE((s->m <= 1 || (s->a_stride % 16 == 0 && s->a_stride >= s->k)) &&
+                (s->n <= 1 || (s->b_stride % 16 == 0 && s->b_stride >= s->k)),
+                "the row strides of a and b must be multiples of 16 bytes and at least k");
+    ZCK_REQUIRE(aligned(out, 16) && (s->m <= 1 || s->out_stride % 8 == 0), "out needs 16-byte aligned rows");
+    ZCK_REQUIRE(!residual || (aligned(residual, 16) && s->residual_stride % 8 == 0), "residual needs 16-byte aligned rows");
+    ZCK_REQUIRE(!bias || aligned(bias, 16), "bias must start at a multiple of 16 bytes");
+    ZCK_REQUIRE(((s->e8m0_bits & 1u) || aligned(scale_a, 4)) && ((s->e8m0_bits & 2u) || aligned(scale_b, 4)),
+                "FP32 scales must be 4-byte aligned");
+    DeviceGuard guard(device);
+    ZCK_CUDA(guard.error);
+    StaticState* state = nullptr;
+    if ((code = static_setup(device, &state)) != ZCK_OK) return code;
+
+    GemmParams p;
+    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_u = nullptr;
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.bias_u = nullptr;
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.parts = reinterpret_cast<float*>(state->base);
+    p.counters = reinterpret_cast<uint32_t*>(state->base + kStaticCounterOffset);
+    p.status = reinterpret_cast<uint32_t*>(state->base + kStaticStatusOffset);
+    p.wait_ns = wait_limit_ns();
+    p.sa_row = s->sa_row; p.sa_blk = s->sa_blk; p.sb_row = s->sb_row; p.sb_blk = s->sb_blk;
+    p.su_row = 0; p.su_blk = 0; p.out_stride = s->out_stride; p.residual_stride = s->residual_stride;
+    p.m = s->m; p.n = s->n; p.k = s->k; p.e8m0_bits = s->e8m0_bits; p.activation = s->activation;
+    tile_counts(*s, false, &p.m_tiles, &p.n_tiles);
+    p.kblocks = s->k / kBK;
+    const uint64_t tiles = (uint64_t)p.m_tiles * p.n_tiles;
+    ZCK_REQUIRE(tiles <= 0x7FFFFFFFull, "too many tiles");
+    // sizes->splits > 1 asks for that many K splits; otherwise the library plans as zck_gemm_plan does.
+    p.splits = s->splits > 1 ? min((uint32_t)s->splits, p.kblocks) : choose_splits((uint32_t)tiles, p.kblocks, state->sm_count);
+    const uint64_t units = tiles * p.splits;
+    ZCK_REQUIRE(units <= 0x7FFFFFFFull, "too many work units");
+    p.units = (uint32_t)units;
+    if (p.splits > 1) {
+        ZCK_REQUIRE(units <= kStaticUnits && tiles <= kStaticCounters,
+                    "this product needs %llu partial tiles and %llu counters of split-K scratch; the static scratch of "
+                    "zck_fp8_gemm_static holds %u tiles (%zu MiB) and %u counters: call zck_fp8_gemm with a workspace",
+                    (unsigned long long)units, (unsigned long long)tiles, kStaticUnits, kStaticPartBytes >> 20,
+                    kStaticCounters);
+    }
+    CUtensorMap map_a, map_b;
+    if ((code = encode_map(a, s->m, s->k, s->a_stride, kBM, &map_a)) != ZCK_OK) return code;
+    if ((code = encode_map(b, s->n, s->k, s->b_stride, kBoxRows, &map_b)) != ZCK_OK) return code;
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    // The scratch keeps the last call's contents: counters (and the record) must start at zero.
+    const size_t clear = kStaticScratchBytes - kStaticCounterOffset;
+    ZCK_CUDA(cudaMemsetAsync(state->base + kStaticCounterOffset, 0, clear, cs));
+    dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
+    fp8_gemm_kernel<false><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_b, p);
+    ZCK_CUDA(cudaGetLastError());
+    return ZCK_OK;
+}
