@@ -90,6 +90,26 @@ def test_config2_sizes_are_bit_exact(ops):
         assert_same_bits(q, eq, "tile codes")
 
 
+@pytest.mark.parametrize("dtype", (torch.float32, BF16))
+def test_wide_dynamic_range_inside_groups_is_bit_exact(ops, dtype):
+    """Values spread over 40 binades inside every group, scales over 80 binades across groups: the quotients land on
+    every kind of E4M3 rounding boundary, underflow and zero, which pins the kernels' division against x / scale."""
+    generator = torch.Generator().manual_seed(17)
+    rows, k = 2048, 1024
+    magnitude = torch.exp2(-40 * torch.rand(rows, k, generator=generator))
+    group_scale = torch.exp2(torch.randint(-40, 41, (rows, k // 128, 1), generator=generator).float())
+    x = (torch.randn(rows, k, generator=generator) * magnitude).reshape(rows, k // 128, 128) * group_scale
+    x = x.reshape(rows, k).to(dtype)
+    q, s = ops.quantize_fp8_rows(x.cuda())
+    eq, es = rules.quantize_rows(x)
+    assert_same_bits(s, es, "row scales")
+    assert_same_bits(q, eq, "row codes")
+    q, s = ops.quantize_fp8_tiles(x.cuda())
+    eq, es = rules.quantize_tiles(x)
+    assert_same_bits(s, es, "tile scales")
+    assert_same_bits(q, eq, "tile codes")
+
+
 def test_quantizers_are_idempotent_on_their_own_output_at_full_size(ops):
     """Size-independent property at the largest hot-path size (16384 x 8192): dequantised codes re-quantize to the
     same codes and scales with power-of-two (E8M0) scales."""

@@ -37,7 +37,7 @@ constexpr int kLaunchRegs = 168, kIdleRegs = 40, kEpilogueRegs = 232;
 static_assert((kLaunchRegs - kIdleRegs) * 128 >= (kEpilogueRegs - kLaunchRegs) * kEpilogueThreads,
               "the epilogue warpgroups would wait forever for registers");
 constexpr uint32_t kTmemColumns = 512;
-constexpr int kBand = 8;  // M tiles that share a band of the tile walk
+constexpr int kBand = 16;  // M tiles that share a band of the tile walk
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
 constexpr int kTileFloats = kBM * kBN;
 
@@ -145,8 +145,19 @@ __device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t un
 
 // Output phase of one thread: 128 accumulators of row `row`. Store tiles: columns col0 .. col0+127. Gated tiles:
 // acc[0..63] are gate sums and acc[64..127] up sums of columns col0 .. col0+63.
+// Element `index` of the 128 accumulators, which live as 64 packed pairs (for the two-wide FP32 FMA).
+__device__ __forceinline__ float acc_at(const float2 (&acc)[64], int index) {
+    return (index & 1) ? acc[index >> 1].y : acc[index >> 1].x;
+}
+
+// Value `i` of eight BF16 values packed in a uint4.
+__device__ __forceinline__ float bf16_at(const uint4& w, int i) {
+    const uint32_t word = i < 2 ? w.x : i < 4 ? w.y : i < 6 ? w.z : w.w;
+    return (i & 1) ? bf16_hi(word) : bf16_lo(word);
+}
+
 template <bool GATED, int ACT>
-__device__ __forceinline__ void write_row(const GemmParams& p, const float (&acc)[128], uint32_t row, uint32_t col0) {
+__device__ __forceinline__ void write_row(const GemmParams& p, const float2 (&acc)[64], uint32_t row, uint32_t col0) {
     constexpr int kColumns = GATED ? 64 : 128;
     __nv_bfloat16* out = p.out + (uint64_t)row * p.out_stride;
     const __nv_bfloat16* residual = p.residual ? p.residual + (uint64_t)row * p.residual_stride : nullptr;
@@ -154,47 +165,60 @@ __device__ __forceinline__ void write_row(const GemmParams& p, const float (&acc
     for (int j = 0; j < kColumns; j += 8) {
         const uint32_t col = col0 + j;
         if (col >= p.n) break;  // n % 8 == 0: an octet is inside or outside as a whole
-        float bias[8], bias_u[8], res[8], y[8];
-        if (p.bias) {
-            uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
-            bias[0] = bf16_lo(w.x); bias[1] = bf16_hi(w.x); bias[2] = bf16_lo(w.y); bias[3] = bf16_hi(w.y);
-            bias[4] = bf16_lo(w.z); bias[5] = bf16_hi(w.z); bias[6] = bf16_lo(w.w); bias[7] = bf16_hi(w.w);
-        } else {
+        // Bias and residual octets either stay packed (four registers each, unpacked value by value) or are widened
+        // to FP32 up front. Which of the two keeps ptxas from spilling inside the K loop differs by instance and was
+        // chosen by measurement: packed for the gated tiles, widened for the store tiles.
+        float y[8];
+        if constexpr (GATED) {
+            uint4 bias = make_uint4(0, 0, 0, 0), bias_u = make_uint4(0, 0, 0, 0), res = make_uint4(0, 0, 0, 0);
+            if (p.bias) bias = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+            if (p.bias_u) bias_u = __ldg(reinterpret_cast<const uint4*>(p.bias_u + col));
+            if (residual) res = ld_global_v4(residual + col);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) bias[i] = 0.0f;
-        }
-        if (GATED) {
-            if (p.bias_u) {
-                uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias_u + col));
-                bias_u[0] = bf16_lo(w.x); bias_u[1] = bf16_hi(w.x); bias_u[2] = bf16_lo(w.y); bias_u[3] = bf16_hi(w.y);
-                bias_u[4] = bf16_lo(w.z); bias_u[5] = bf16_hi(w.z); bias_u[6] = bf16_lo(w.w); bias_u[7] = bf16_hi(w.w);
+            for (int i = 0; i < 8; ++i) {
+                float t = bf16_round(__fadd_rn(acc_at(acc, j + i), bf16_at(bias, i)));
+                float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
+                float v = bf16_round(__fadd_rn(acc_at(acc, 64 + j + i), bf16_at(bias_u, i)));
+                u = bf16_round(__fmul_rn(u, v));
+                y[i] = residual ? __fadd_rn(u, bf16_at(res, i)) : u;
+            }
+        } else {
+            float wide_bias[8], wide_res[8];
+            if (p.bias) {
+                uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                wide_bias[0] = bf16_lo(w.x); wide_bias[1] = bf16_hi(w.x); wide_bias[2] = bf16_lo(w.y); wide_bias[3] = bf16_hi(w.y);
+                wide_bias[4] = bf16_lo(w.z); wide_bias[5] = bf16_hi(w.z); wide_bias[6] = bf16_lo(w.w); wide_bias[7] = bf16_hi(w.w);
             } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) bias_u[i] = 0.0f;
+                for (int i = 0; i < 8; ++i) wide_bias[i] = 0.0f;
             }
-        }
-        if (residual) {
-            uint4 w = ld_global_v4(residual + col);
-            res[0] = bf16_lo(w.x); res[1] = bf16_hi(w.x); res[2] = bf16_lo(w.y); res[3] = bf16_hi(w.y);
-            res[4] = bf16_lo(w.z); res[5] = bf16_hi(w.z); res[6] = bf16_lo(w.w); res[7] = bf16_hi(w.w);
-        }
+            if (residual) {
+                uint4 w = ld_global_v4(residual + col);
+                wide_res[0] = bf16_lo(w.x); wide_res[1] = bf16_hi(w.x); wide_res[2] = bf16_lo(w.y); wide_res[3] = bf16_hi(w.y);
+                wide_res[4] = bf16_lo(w.z); wide_res[5] = bf16_hi(w.z); wide_res[6] = bf16_lo(w.w); wide_res[7] = bf16_hi(w.w);
+            }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            float t = bf16_round(__fadd_rn(acc[j + i], bias[i]));
-            float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
-            if constexpr (GATED) {
-                float v = bf16_round(__fadd_rn(acc[64 + j + i], bias_u[i]));
-                u = bf16_round(__fmul_rn(u, v));
+            for (int i = 0; i < 8; ++i) {
+                float t = bf16_round(__fadd_rn(acc_at(acc, j + i), wide_bias[i]));
+                float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
+                y[i] = residual ? __fadd_rn(u, wide_res[i]) : u;
             }
-            y[i] = residual ? __fadd_rn(u, res[i]) : u;
         }
         st_global_v4(out + col, make_uint4(bf16x2_of(y[0], y[1]), bf16x2_of(y[2], y[3]), bf16x2_of(y[4], y[5]),
                                            bf16x2_of(y[6], y[7])));
     }
 }
 
-template <bool GATED>
-__device__ __forceinline__ void write_row_any(const GemmParams& p, const float (&acc)[128], uint32_t row, uint32_t col0) {
+// ACT >= 0 names the activation at compile time (one output phase in the kernel: no spills); ACT < 0 picks at run
+// time (the split-K instances, which are bound by memory, not by registers).
+constexpr int kActAny = -1;
+
+template <bool GATED, int ACT>
+__device__ __forceinline__ void write_row_any(const GemmParams& p, const float2 (&acc)[64], uint32_t row, uint32_t col0) {
+    if constexpr (ACT >= 0) {
+        write_row<GATED, ACT>(p, acc, row, col0);
+        return;
+    }
     switch (p.activation) {
         case ZCK_ACT_SILU: write_row<GATED, ZCK_ACT_SILU>(p, acc, row, col0); break;
         case ZCK_ACT_GELU_TANH: write_row<GATED, ZCK_ACT_GELU_TANH>(p, acc, row, col0); break;
@@ -203,7 +227,8 @@ __device__ __forceinline__ void write_row_any(const GemmParams& p, const float (
     }
 }
 
-template <bool GATED>
+// SPLIT instances carry the split-K exchange; keeping it out of the others keeps their epilogue in registers.
+template <bool GATED, bool SPLIT, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_u, const GemmParams p) {
@@ -324,42 +349,65 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             // Output columns of this thread and the weight scale tile they fall in.
             const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);
             const uint32_t scale_tile = min(col0 / kGroup, (p.n - 1) / kGroup);
-            float acc[128];
+            float2 acc[64];
 #pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] = 0.0f;
-            float sa_next = row_live ? load_scale(p.scale_a, (uint64_t)row * p.sa_row + (uint64_t)c.kb0 * p.sa_blk, sa_e8m0) : 0.0f;
+            for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
+            // Scales are fetched one K block ahead, so that no load sits between a full buffer and its drain.
+            const uint64_t sa_base = (uint64_t)row * p.sa_row, sb_base = (uint64_t)scale_tile * p.sb_row,
+                           su_base = (uint64_t)scale_tile * p.su_row;
+            float sa_next = row_live ? load_scale(p.scale_a, sa_base + (uint64_t)c.kb0 * p.sa_blk, sa_e8m0) : 0.0f;
+            float sb_next = load_scale(p.scale_b, sb_base + (uint64_t)c.kb0 * p.sb_blk, sb_e8m0);
+            float su_next = GATED ? load_scale(p.scale_u, su_base + (uint64_t)c.kb0 * p.su_blk, su_e8m0) : 0.0f;
             for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
                 const uint32_t kb = c.kb0 + i;
                 const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
-                const float sa = sa_next;
-                if (row_live && i + 1 < c.kb_count)
-                    sa_next = load_scale(p.scale_a, (uint64_t)row * p.sa_row + (uint64_t)(kb + 1) * p.sa_blk, sa_e8m0);
-                const float f0 = __fmul_rn(sa, load_scale(p.scale_b, (uint64_t)scale_tile * p.sb_row + (uint64_t)kb * p.sb_blk, sb_e8m0));
-                const float f1 = GATED ? __fmul_rn(sa, load_scale(p.scale_u, (uint64_t)scale_tile * p.su_row + (uint64_t)kb * p.su_blk, su_e8m0)) : f0;
+                const float f0 = __fmul_rn(sa_next, sb_next);
+                const float f1 = GATED ? __fmul_rn(sa_next, su_next) : f0;
+                if (i + 1 < c.kb_count) {
+                    if (row_live) sa_next = load_scale(p.scale_a, sa_base + (uint64_t)(kb + 1) * p.sa_blk, sa_e8m0);
+                    sb_next = load_scale(p.scale_b, sb_base + (uint64_t)(kb + 1) * p.sb_blk, sb_e8m0);
+                    if (GATED) su_next = load_scale(p.scale_u, su_base + (uint64_t)(kb + 1) * p.su_blk, su_e8m0);
+                }
                 if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, kb))) break;
                 ptx::tc_fence_after();
                 if (warp_live) {
+                    // Drain in four chunks of 32 columns through two register buffers: the loads of chunks 2 and 3
+                    // are in flight while chunks 0 and 1 are folded in, and the buffer goes back to the tensor core
+                    // as soon as the last load has landed, before the last FMAs.
                     const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + group * 128u;
+                    const float2 f0x2 = make_float2(f0, f0), f1x2 = make_float2(f1, f1);
+                    uint32_t even[32], odd[32];
+                    ptx::tmem_ld_32x32(taddr, even);
+                    ptx::tmem_ld_32x32(taddr + 32, odd);
+                    ptx::tmem_wait_ld();
 #pragma unroll
-                    for (int chunk = 0; chunk < 4; ++chunk) {
-                        uint32_t product[32];
-                        ptx::tmem_ld_32x32(taddr + chunk * 32, product);
-                        ptx::tmem_wait_ld();
-                        const float f = chunk < 2 ? f0 : f1;
+                    for (int j = 0; j < 16; ++j)
+                        acc[j] = __ffma2_rn(make_float2(__uint_as_float(even[2 * j]), __uint_as_float(even[2 * j + 1])), f0x2, acc[j]);
+                    ptx::tmem_ld_32x32_reuse(taddr + 64, even);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            acc[chunk * 32 + j] = __fmaf_rn(__uint_as_float(product[j]), f, acc[chunk * 32 + j]);
-                    }
+                    for (int j = 0; j < 16; ++j)
+                        acc[16 + j] = __ffma2_rn(make_float2(__uint_as_float(odd[2 * j]), __uint_as_float(odd[2 * j + 1])), f0x2, acc[16 + j]);
+                    ptx::tmem_ld_32x32_reuse(taddr + 96, odd);
+                    ptx::tmem_wait_ld();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(even[2 * j]), __uint_as_float(even[2 * j + 1])), f1x2, acc[32 + j]);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(odd[2 * j]), __uint_as_float(odd[2 * j + 1])), f1x2, acc[48 + j]);
+                } else {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
                 }
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
             }
             if (!ok) break;
-            if (p.splits == 1) {
-                if (row_live) write_row_any<GATED>(p, acc, row, col0);
-                continue;
-            }
+            if constexpr (!SPLIT) {
+                if (row_live) write_row_any<GATED, ACT>(p, acc, row, col0);
+            } else {
             // Split K: every split stores its partial tile; the split that arrives last adds all of them in split
             // order (so the bits do not depend on who was last), runs the epilogue and re-arms the counter.
             // Part layout per unit: [group][column quad][row][4 floats], so that a warp stores 512 contiguous bytes.
@@ -368,7 +416,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                 for (int quad = 0; quad < 32; ++quad)
                     __stcg(reinterpret_cast<float4*>(part + (uint64_t)quad * kBM * 4),
-                           make_float4(acc[4 * quad], acc[4 * quad + 1], acc[4 * quad + 2], acc[4 * quad + 3]));
+                           make_float4(acc[2 * quad].x, acc[2 * quad].y, acc[2 * quad + 1].x, acc[2 * quad + 1].y));
             }
             __threadfence();
             ptx::named_barrier(1, kEpilogueThreads);
@@ -391,10 +439,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
                         sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
                     }
-                    acc[4 * quad] = sum.x; acc[4 * quad + 1] = sum.y; acc[4 * quad + 2] = sum.z; acc[4 * quad + 3] = sum.w;
+                    acc[2 * quad] = make_float2(sum.x, sum.y); acc[2 * quad + 1] = make_float2(sum.z, sum.w);
                 }
-                write_row_any<GATED>(p, acc, row, col0);
+                write_row_any<GATED, ACT>(p, acc, row, col0);
             }
+            }  // SPLIT
         }
     }
     ptx::tc_fence_before();
@@ -459,6 +508,29 @@ static int tensor_map_of(const void* base, uint64_t rows, uint64_t k, uint64_t s
     return ZCK_OK;
 }
 
+typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+// Kernel instance for a launch: the activation is a compile-time constant except in the split-K instances.
+static GemmKernel kernel_for(bool gated, bool split, int activation) {
+    if (split) return gated ? fp8_gemm_kernel<true, true, kActAny> : fp8_gemm_kernel<false, true, kActAny>;
+    switch (activation) {
+        case ZCK_ACT_SILU: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_SILU> : fp8_gemm_kernel<false, false, ZCK_ACT_SILU>;
+        case ZCK_ACT_GELU_TANH: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_GELU_TANH> : fp8_gemm_kernel<false, false, ZCK_ACT_GELU_TANH>;
+        case ZCK_ACT_GELU: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_GELU> : fp8_gemm_kernel<false, false, ZCK_ACT_GELU>;
+        default: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_NONE> : fp8_gemm_kernel<false, false, ZCK_ACT_NONE>;
+    }
+}
+
+static int raise_shared_memory_limits() {
+    for (int gated = 0; gated < 2; ++gated) {
+        ZCK_CUDA(cudaFuncSetAttribute(kernel_for(gated, true, 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        for (int activation = ZCK_ACT_NONE; activation <= ZCK_ACT_GELU; ++activation)
+            ZCK_CUDA(cudaFuncSetAttribute(kernel_for(gated, false, activation), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kSmemBytes));
+    }
+    return ZCK_OK;
+}
+
 int init_gemm(int device) {
     (void)device;
     if (!g_encode) {
@@ -469,9 +541,7 @@ int init_gemm(int device) {
             return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
         g_encode = reinterpret_cast<EncodeTiled>(entry);
     }
-    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-    return ZCK_OK;
+    return raise_shared_memory_limits();
 }
 
 static uint64_t wait_limit_ns() {
@@ -565,8 +635,7 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
 
     dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    if (gated) fp8_gemm_kernel<true><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
-    else fp8_gemm_kernel<false><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
+    kernel_for(gated, p.splits > 1, p.activation)<<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }
@@ -659,6 +728,7 @@ static int static_setup(int device, StaticState** out) {
     if (major != 10) return fail(ZCK_ERR_UNSUPPORTED, "device %d is not an sm_100 device", device);
     ZCK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
     void* address = nullptr;
+    int code = ZCK_OK;
     ZCK_CUDA(cudaGetSymbolAddress(&address, g_static_scratch));
     if (!g_encode) {
         void* entry = nullptr;
@@ -668,7 +738,7 @@ static int static_setup(int device, StaticState** out) {
             return fail(ZCK_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
         g_encode = reinterpret_cast<EncodeTiled>(entry);
     }
-    ZCK_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+    if ((code = raise_shared_memory_limits()) != ZCK_OK) return code;
     state->base = static_cast<unsigned char*>(address);
     state->sm_count = sms;
     state->ready = true;
@@ -748,7 +818,7 @@ extern "C" int zck_fp8_gemm_static(const void* a, const void* b, const void* sca
     const size_t clear = kStaticScratchBytes - kStaticCounterOffset;
     ZCK_CUDA(cudaMemsetAsync(state->base + kStaticCounterOffset, 0, clear, cs));
     dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
-    fp8_gemm_kernel<false><<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_b, p);
+    kernel_for(false, p.splits > 1, p.activation)<<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_b, p);
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }

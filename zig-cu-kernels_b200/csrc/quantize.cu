@@ -46,11 +46,10 @@ __device__ __forceinline__ float octet_amax(const Octet<T>& o, float amax) {
 
 // Codes of one octet. FP32 scale: x / scale; E8M0 scale: x * 2^(127-b), the same real number, correctly rounded.
 template <typename T, bool E8M0>
-__device__ __forceinline__ uint2 octet_codes(const Octet<T>& o, float divisor_or_factor) {
+__device__ __forceinline__ uint2 octet_codes(const Octet<T>& o, const GroupDivider& divide) {
     float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        q[i] = E8M0 ? __fmul_rn(o.get(i), divisor_or_factor) : __fdiv_rn(o.get(i), divisor_or_factor);
+    for (int i = 0; i < 8; ++i) q[i] = E8M0 ? __fmul_rn(o.get(i), divide.scale) : divide(o.get(i));
     return make_uint2(e4m3x4_of(q[0], q[1], q[2], q[3]), e4m3x4_of(q[4], q[5], q[6], q[7]));
 }
 
@@ -91,9 +90,11 @@ quantize_rows_kernel(const T* __restrict__ x, uint64_t x_stride, uint8_t* __rest
         if (live && lane == 0) static_cast<float*>(scales)[(uint64_t)g * scale_stride + row] = operand;
     }
     if (live) {
+        // For E8M0 the "divider" only carries the power-of-two factor 2^(127-b) that multiplies every value.
+        const GroupDivider divide = GroupDivider::of(operand);
         uint8_t* target = codes + ((uint64_t)row * groups_per_row + g) * kGroup;
-        st_global_v2(target + 8 * lane, octet_codes<T, E8M0>(o0, operand));
-        st_global_v2(target + 8 * (8 + lane), octet_codes<T, E8M0>(o1, operand));
+        st_global_v2(target + 8 * lane, octet_codes<T, E8M0>(o0, divide));
+        st_global_v2(target + 8 * (8 + lane), octet_codes<T, E8M0>(o1, divide));
     }
 }
 
@@ -137,11 +138,12 @@ quantize_tiles_kernel(const T* __restrict__ w, uint64_t w_stride, uint8_t* __res
         operand = scale_f32_of(amax);
         if (threadIdx.x == 0) static_cast<float*>(scales)[(uint64_t)tile_row * scale_stride + tile_col] = operand;
     }
+    const GroupDivider divide = GroupDivider::of(operand);
     uint8_t* target = codes + (uint64_t)first_row * k + (uint64_t)tile_col * kGroup + 8 * o;
 #pragma unroll
     for (int pass = 0; pass < 8; ++pass) {
         uint32_t row = pass * 16 + r;
-        if (first_row + row < n) st_global_v2(target + (uint64_t)row * k, octet_codes<T, E8M0>(held[pass], operand));
+        if (first_row + row < n) st_global_v2(target + (uint64_t)row * k, octet_codes<T, E8M0>(held[pass], divide));
     }
 }
 

@@ -57,6 +57,36 @@ __device__ __forceinline__ float e8m0_reciprocal(uint32_t byte) {
     return e8m0_to_f32(byte == 255u ? 255u : 254u - byte);
 }
 
+// x / scale for every value of one scale group, bit-identical to div.rn.f32 but three instructions per value.
+// With r = RN(1/scale), q = RN(x * r) is within one ulp of the quotient, the FMA gives the exact remainder
+// x - q * scale, and RN(q + remainder * r) is the correctly rounded quotient (Markstein). That argument needs the
+// remainder to be representable, which holds wherever the E4M3 code is not zero when 2^-60 <= scale <= 2^60 (all
+// values of a group are at most 448 * scale); groups outside that range, or with an infinite or NaN scale, take the
+// plain division.
+struct GroupDivider {
+    float scale, reciprocal;
+    bool fast;
+    static __device__ __forceinline__ GroupDivider of(float s) {
+        GroupDivider d;
+        d.scale = s;
+        d.reciprocal = __frcp_rn(s);
+        const uint32_t exponent = (__float_as_uint(s) >> 23) & 0xFFu;
+        d.fast = exponent >= 127u - 60u && exponent <= 127u + 60u;
+        return d;
+    }
+    __device__ __forceinline__ float operator()(float x) const {
+        if (fast) {
+            const float q = __fmul_rn(x, reciprocal);
+            const float remainder = __fmaf_rn(-q, scale, x);
+            const float rounded = __fmaf_rn(remainder, reciprocal, q);
+            // The scale is positive, so the quotient has the sign of x; the correction step alone would turn an
+            // exact -0 into +0 (a zero remainder is +0).
+            return __uint_as_float((__float_as_uint(rounded) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
+        }
+        return __fdiv_rn(x, scale);
+    }
+};
+
 // Two FP32 values to two E4M3 bytes: round to nearest even, magnitudes above 448 clamp to 448, NaN gives 0x7F.
 // `lo` lands in bits 0-7 and `hi` in bits 8-15.
 __device__ __forceinline__ uint32_t e4m3x2_of(float lo, float hi) {
