@@ -1,0 +1,52 @@
+"""Run under torchrun on N GPUs: the tensor-parallel MLP against the one-GPU MLP on the same seeded tensors.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P tests/tp_check.py
+"""
+
+import os
+import pathlib
+import sys
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+sys.path[:0] = [str(ROOT / "zig-cu-kernels_b200"), str(ROOT)]
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from zig_cu_kernels.tp_mlp import TensorParallelMLP, exchange_plan  # noqa: E402
+
+
+def main():
+    world, rank, local = (int(os.environ[name]) for name in ("WORLD_SIZE", "RANK", "LOCAL_RANK"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=device)
+    generator = torch.Generator(device=device).manual_seed(4)
+    m, hidden, inter = 2048, 1024, 4096
+    tokens = torch.randn(m, hidden, device=device, generator=generator).bfloat16()
+    w_gate = (torch.randn(inter, hidden, device=device, generator=generator) / 32).bfloat16()
+    w_up = (torch.randn(inter, hidden, device=device, generator=generator) / 32).bfloat16()
+    w_down = (torch.randn(hidden, inter, device=device, generator=generator) / 64).bfloat16()
+    whole = TensorParallelMLP(w_gate, w_up, w_down).forward(tokens).float()
+    worst = 0.0
+    for exchange, chunks in (("all_reduce", 1), ("all_reduce", 4), ("reduce_scatter", 2)):
+        mlp = TensorParallelMLP(w_gate, w_up, w_down, rank, world, chunks=chunks, exchange=exchange)
+        result = mlp.forward(tokens).float()
+        torch.cuda.synchronize()
+        if exchange == "all_reduce":
+            expected = whole
+        else:
+            plan = exchange_plan(m, world, chunks, exchange)
+            expected = torch.cat([whole[lo:hi].chunk(world)[rank] for lo, hi, _, _ in plan])
+        error = float((result - expected).abs().max() / whole.abs().max())
+        worst = max(worst, error)
+        assert error <= 1e-2, f"rank {rank} {exchange} chunks={chunks}: max relative error {error}"
+    errors = torch.tensor([worst], device=device)
+    dist.all_reduce(errors, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"TP_CHECK_OK world={world} max_relative_error={float(errors):.3e}")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

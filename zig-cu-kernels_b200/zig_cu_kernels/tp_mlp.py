@@ -24,13 +24,34 @@ def shard_bounds(inter, rank, world):
     return rank * step, (rank + 1) * step
 
 
+def exchange_plan(m, world, chunks, exchange):
+    """Row ranges of the token chunks and, for reduce_scatter, where each chunk's share lands in this rank's result:
+    a list of `(lo, hi, result_lo, result_hi)`. all_reduce reduces `partial[lo:hi]` in place (result range = chunk
+    range); reduce_scatter needs chunk row counts that are multiples of `world` and packs the shares chunk after
+    chunk. Chunks are at least `world * 128` rows, so the requested count is only an upper bound."""
+    if exchange not in ("all_reduce", "reduce_scatter"):
+        raise ValueError("exchange must be all_reduce or reduce_scatter")
+    chunks = max(1, min(chunks, m // (world * GROUP) or 1))
+    bounds = [m * c // chunks for c in range(chunks + 1)]
+    plan, offset = [], 0
+    for lo, hi in zip(bounds, bounds[1:]):
+        if exchange == "all_reduce":
+            plan.append((lo, hi, lo, hi))
+            continue
+        if (hi - lo) % world:
+            raise ValueError("reduce_scatter needs chunk row counts that are multiples of the world size")
+        rows = (hi - lo) // world
+        plan.append((lo, hi, offset, offset + rows))
+        offset += rows
+    return plan
+
+
 class TensorParallelMLP:
     """Holds this rank's quantized weight shards and runs the forward pass of its share."""
 
     def __init__(self, w_gate, w_up, w_down, rank=0, world=1, group=None, scale_dtype=torch.float32, chunks=1,
                  exchange="all_reduce"):
-        if exchange not in ("all_reduce", "reduce_scatter"):
-            raise ValueError("exchange must be all_reduce or reduce_scatter")
+        exchange_plan(GROUP, 1, 1, exchange)  # validates the name
         inter, hidden = w_gate.shape
         if tuple(w_up.shape) != (inter, hidden) or tuple(w_down.shape) != (hidden, inter):
             raise ValueError("w_gate and w_up must be [I, H] and w_down [H, I]")
@@ -72,24 +93,18 @@ class TensorParallelMLP:
         m = tokens.shape[0]
         if self.world == 1:
             return self.partial(tokens)
-        chunks = max(1, min(self.chunks, m // (self.world * GROUP) or 1))
-        bounds = [m * c // chunks for c in range(chunks + 1)]
+        plan = exchange_plan(m, self.world, self.chunks, self.exchange)
         scatter = self.exchange == "reduce_scatter"
-        if scatter and any((hi - lo) % self.world for lo, hi in zip(bounds, bounds[1:])):
-            raise ValueError("reduce_scatter needs chunk row counts that are multiples of the world size")
         partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=tokens.device)
         result = torch.empty(m // self.world, self.hidden, dtype=torch.bfloat16, device=tokens.device) if scatter \
             else partial
         compute = torch.cuda.current_stream()
-        offset = 0
-        for lo, hi in zip(bounds, bounds[1:]):
+        for lo, hi, result_lo, result_hi in plan:
             self.partial(tokens[lo:hi], out=partial[lo:hi])
             self.comm_stream.wait_stream(compute)
             with torch.cuda.stream(self.comm_stream):
                 if scatter:
-                    rows = (hi - lo) // self.world
-                    dist.reduce_scatter_tensor(result[offset:offset + rows], partial[lo:hi], group=self.group)
-                    offset += rows
+                    dist.reduce_scatter_tensor(result[result_lo:result_hi], partial[lo:hi], group=self.group)
                 else:
                     dist.all_reduce(partial[lo:hi], group=self.group)
         compute.wait_stream(self.comm_stream)
