@@ -140,9 +140,9 @@ def run_reference(args):
     }))
 
 
-def workload_config(gpus):
+def workload_config(gpus, exchange="reduce_scatter"):
     return {"workload": f"llama70b_swiglu_mlp_prefill M={M} H={HIDDEN} I={INTER} fp32 block128 scales (BASELINE config 5)",
-            "global_batch_tokens": M, "parallelism": f"tp{gpus}", "exchange": "all_reduce",
+            "global_batch_tokens": M, "parallelism": f"tp{gpus}", "exchange": exchange if gpus > 1 else "none",
             "l2": "weights (705 MB FP8) and activations exceed the 126 MB L2, no flush needed"}
 
 
@@ -152,7 +152,9 @@ def main():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    parser.add_argument("--chunks", type=int, default=4, help="token chunks whose exchange overlaps the next GEMMs")
+    parser.add_argument("--chunks", type=int, default=1, help="token chunks whose exchange overlaps the next GEMMs")
+    parser.add_argument("--exchange", default="reduce_scatter", choices=("reduce_scatter", "all_reduce"))
+    parser.add_argument("--no-graphs", action="store_true", help="launch every op from Python instead of replaying CUDA graphs")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--tokens", type=int, default=M, help="token rows per step (smaller only for profiling)")
     args = parser.parse_args()
@@ -182,22 +184,49 @@ def main():
         torch.cuda.synchronize()
 
     tokens, w_gate, w_up, w_down = synthetic(device, rows=tokens_per_step)
-    mlp = TensorParallelMLP(w_gate, w_up, w_down, rank, world, chunks=args.chunks if world > 1 else 1)
+    mlp = TensorParallelMLP(w_gate, w_up, w_down, rank, world, chunks=args.chunks if world > 1 else 1,
+                            exchange=args.exchange)
     del w_gate, w_up, w_down
     torch.cuda.empty_cache()
-    pinned_in = torch.empty(tokens.shape, dtype=tokens.dtype).pin_memory()
-    pinned_in.copy_(tokens)
-    pinned_out = torch.empty(tokens.shape, dtype=tokens.dtype).pin_memory()
+    # End-to-end step: every rank owns tokens_per_step / world rows in pinned host memory, copies them to the device,
+    # the ranks all-gather the token matrix over NVLink, run the MLP and each reads back what the exchange left it
+    # (its rows after reduce_scatter, all rows after all_reduce).
+    own = tokens_per_step // world
+    own_lo = rank * own
+    pinned_in = torch.empty(own, HIDDEN, dtype=tokens.dtype).pin_memory()
+    pinned_in.copy_(tokens[own_lo:own_lo + own])
+    out_rows = own if (world > 1 and args.exchange == "reduce_scatter") else tokens_per_step
+    pinned_out = torch.empty(out_rows, HIDDEN, dtype=tokens.dtype).pin_memory()
     staged = torch.empty_like(tokens)
+    staged_own = staged[own_lo:own_lo + own] if world == 1 else torch.empty(own, HIDDEN, dtype=tokens.dtype, device=device)
 
-    def device_step():
+    def upload():
+        staged_own.copy_(pinned_in, non_blocking=True)
+
+    def download(result):
+        pinned_out.copy_(result, non_blocking=True)
+
+    if args.no_graphs:
+        def device_step():
+            return mlp.forward(tokens)
+
+        def e2e_step():
+            upload()
+            result = mlp.forward(staged, staged_own)
+            download(result)
+            return result
+    else:
+        device_step = mlp.graphed(tokens)
+        replay_staged = mlp.graphed(staged)
+
+        def e2e_step():
+            upload()
+            result = replay_staged(staged_own)
+            download(result)
+            return result
+
+    def eager_step():
         return mlp.forward(tokens)
-
-    def e2e_step():
-        staged.copy_(pinned_in, non_blocking=True)
-        result = mlp.forward(staged)
-        pinned_out[: result.shape[0]].copy_(result, non_blocking=True)
-        return result
 
     def timed(step, steps):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -217,15 +246,18 @@ def main():
         device_step()
         e2e_step()
     barrier()
-    launches_before = mlp.launches
-    mlp.kernel_events = {}
     wall_begin = time.time()
     device_seconds = timed(device_step, args.steps)
     wall_end = time.time()
-    events, mlp.kernel_events = mlp.kernel_events, None
-    launches = mlp.launches - launches_before
     e2e_seconds = timed(e2e_step, args.steps)
     clocks = sampler.stop(wall_begin, wall_end) if sampler else None
+    # Kernel durations for the roofline: the same K steps once more, launched op by op with CUDA events around each
+    # kernel (events cannot sit inside a replayed graph).
+    launches_before = mlp.launches
+    mlp.kernel_events = {}
+    timed(eager_step, args.steps)
+    events, mlp.kernel_events = mlp.kernel_events, None
+    launches = mlp.launches - launches_before  # the kernels of one pass of K steps (a replay launches the same)
 
     kernel_ms = {name: statistics.mean(start.elapsed_time(end) for start, end in pairs) for name, pairs in events.items()}
     launches_per_step = {name: len(pairs) // args.steps for name, pairs in events.items()}
@@ -248,11 +280,12 @@ def main():
         "metric": "tp_mlp_tokens_per_s", "value": tokens_per_step * args.steps / device_seconds, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": device_seconds / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
-        "config": dict(workload_config(world), tokens_per_step=tokens_per_step),
+        "config": dict(workload_config(world, args.exchange), tokens_per_step=tokens_per_step, chunks=args.chunks,
+                       launch="python ops" if args.no_graphs else "cuda graph replay of the kernels, NCCL calls between replays"),
         "tflops": tokens_per_step * FLOPS_PER_TOKEN * args.steps / device_seconds / 1e12,
         "e2e": {"value": tokens_per_step * args.steps / e2e_seconds, "unit": "tokens/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
-                "h2d_bytes_per_step": tokens.numel() * 2,
-                "d2h_bytes_per_step": tokens.numel() * 2},
+                "h2d_bytes_per_step": own * HIDDEN * 2 * world,
+                "d2h_bytes_per_step": out_rows * HIDDEN * 2 * world},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"kernel": "fp8_gemm_kernel<gated> (fp8_gated_gemm)", "bound": "tensor", "achieved": gated_tflops,

@@ -85,14 +85,20 @@ class TensorParallelMLP:
         q, scale_q = self._run("quantize_act", ops.quantize_fp8_rows, act, scale_dtype=self.scale_dtype)
         return self._run("down_gemm", ops.fp8_gemm, q, self.down, scale_q, self.scale_down, out=out)
 
-    def forward(self, tokens):
+    def forward(self, tokens, own_rows=None):
         """`(m, H)` BF16 result: the full sum on every rank (all_reduce) or this rank's `m/world` rows
-        (reduce_scatter). With one rank this is the plain MLP."""
+        (reduce_scatter). With one rank this is the plain MLP. When `own_rows` is given (this rank's `m/world` rows
+        of the tokens), `tokens` is first filled by an all-gather over NVLink, so that each rank has to bring only
+        its own rows onto the device."""
         import torch.distributed as dist
 
         m = tokens.shape[0]
         if self.world == 1:
+            if own_rows is not None and own_rows.data_ptr() != tokens.data_ptr():
+                tokens.copy_(own_rows)
             return self.partial(tokens)
+        if own_rows is not None:
+            dist.all_gather_into_tensor(tokens, own_rows, group=self.group)
         plan = exchange_plan(m, self.world, self.chunks, self.exchange)
         scatter = self.exchange == "reduce_scatter"
         partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=tokens.device)
@@ -109,3 +115,57 @@ class TensorParallelMLP:
                     dist.all_reduce(partial[lo:hi], group=self.group)
         compute.wait_stream(self.comm_stream)
         return result
+
+    def graphed(self, tokens):
+        """Binds a replayable forward pass to the fixed buffer `tokens`: the four kernels of every token chunk are
+        captured into one CUDA graph per chunk (one host launch instead of four op calls), while the collectives
+        stay ordinary NCCL calls between the replays. Returns `replay(own_rows=None) -> result`, same meaning as
+        `forward`. Kernel events cannot be collected from replays."""
+        m = tokens.shape[0]
+        scatter = self.world > 1 and self.exchange == "reduce_scatter"
+        plan = exchange_plan(m, self.world, self.chunks if self.world > 1 else 1, self.exchange)
+        partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=tokens.device)
+        result = torch.empty(m // self.world, self.hidden, dtype=torch.bfloat16, device=tokens.device) if scatter \
+            else partial
+        events, self.kernel_events = self.kernel_events, None
+        current = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(current)
+        with torch.cuda.stream(side):  # eager warm-up off the default stream, as graph capture requires
+            for lo, hi, _, _ in plan:
+                self.partial(tokens[lo:hi], out=partial[lo:hi])
+        current.wait_stream(side)
+        torch.cuda.synchronize()
+        graphs = []
+        for lo, hi, _, _ in plan:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.partial(tokens[lo:hi], out=partial[lo:hi])
+            graphs.append(graph)
+        self.kernel_events = events
+
+        def replay(own_rows=None):
+            import torch.distributed as dist
+
+            if own_rows is not None:
+                if self.world > 1:
+                    dist.all_gather_into_tensor(tokens, own_rows, group=self.group)
+                elif own_rows.data_ptr() != tokens.data_ptr():
+                    tokens.copy_(own_rows)
+            compute = torch.cuda.current_stream()
+            for graph, (lo, hi, result_lo, result_hi) in zip(graphs, plan):
+                graph.replay()
+                self.launches += 4
+                if self.world == 1:
+                    continue
+                self.comm_stream.wait_stream(compute)
+                with torch.cuda.stream(self.comm_stream):
+                    if scatter:
+                        dist.reduce_scatter_tensor(result[result_lo:result_hi], partial[lo:hi], group=self.group)
+                    else:
+                        dist.all_reduce(partial[lo:hi], group=self.group)
+            if self.world > 1:
+                compute.wait_stream(self.comm_stream)
+            return result
+
+        return replay
