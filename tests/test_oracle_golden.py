@@ -116,3 +116,45 @@ def test_sharded_mlp_partials_sum_to_the_unsharded_mlp():
         total = sum(rules.mlp_shard(tokens, w_gate, w_up, w_down, rank, world).float() for rank in range(world))
         error = (total - whole).abs().max() / whole.abs().max()
         assert error < 1e-2, (world, float(error))
+
+
+def c_oracle():
+    import ctypes
+
+    from oracle import build as oracle_build
+
+    lib = ctypes.CDLL(str(oracle_build.build()))
+    lib.zck_oracle_e4m3.restype, lib.zck_oracle_e4m3.argtypes = ctypes.c_uint8, [ctypes.c_float]
+    for name in ("zck_oracle_quantize_rows", "zck_oracle_quantize_tiles"):
+        getattr(lib, name).restype = None
+        getattr(lib, name).argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                       ctypes.c_void_p, ctypes.c_int]
+    return lib
+
+
+def test_c_restatement_matches_the_reference_vectors(golden):
+    """The plain-C restatement (own E4M3 rounding) against the same golden vectors."""
+    lib, g = c_oracle(), golden["quantizers"]
+    every_bf16 = torch.arange(-(1 << 15), 1 << 15, dtype=torch.int32).to(torch.int16).view(BF16).float()
+    codes = torch.tensor([lib.zck_oracle_e4m3(float(v)) for v in every_bf16.tolist()], dtype=torch.uint8)
+    assert_same_bits(codes.view(FP8), every_bf16.clamp(-448, 448).to(FP8), "e4m3 of every BF16 value")
+    for tag, dtype in INPUTS.items():
+        x = from_golden(g[f"rows_x_{tag}"], dtype).float().contiguous()
+        m, k = x.shape
+        for stag, scale_dtype in SCALES.items():
+            codes = torch.empty(m, k, dtype=torch.uint8)
+            scales = torch.empty(k // 128, m, dtype=torch.uint8 if scale_dtype == E8M0 else torch.float32)
+            lib.zck_oracle_quantize_rows(x.data_ptr(), m, k, codes.data_ptr(), scales.data_ptr(), int(scale_dtype == E8M0))
+            expected_scales = from_golden(g[f"rows_scales_{tag}_{stag}"], scale_dtype)
+            got = scales.view(E8M0).t() if scale_dtype == E8M0 else scales.t()
+            assert_same_bits(got.contiguous(), expected_scales, f"C row scales {tag} {stag}")
+            assert_same_bits(codes.view(FP8), from_golden(g[f"rows_codes_{tag}_{stag}"], FP8), f"C row codes {tag} {stag}")
+    for n in (136, 200):
+        w = from_golden(g[f"tiles{n}_w_f32"], torch.float32).contiguous()
+        for stag, scale_dtype in SCALES.items():
+            codes = torch.empty(n, 384, dtype=torch.uint8)
+            scales = torch.empty(2, 3, dtype=torch.uint8 if scale_dtype == E8M0 else torch.float32)
+            lib.zck_oracle_quantize_tiles(w.data_ptr(), n, 384, codes.data_ptr(), scales.data_ptr(), int(scale_dtype == E8M0))
+            got = scales.view(E8M0) if scale_dtype == E8M0 else scales
+            assert_same_bits(got, from_golden(g[f"tiles{n}_scales_f32_{stag}"], scale_dtype), f"C tile scales {n} {stag}")
+            assert_same_bits(codes.view(FP8), from_golden(g[f"tiles{n}_codes_f32_{stag}"], FP8), f"C tile codes {n} {stag}")

@@ -39,6 +39,13 @@ static_assert((kLaunchRegs - kIdleRegs) * 128 >= (kEpilogueRegs - kLaunchRegs) *
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kBand = 16;  // M tiles that share a band of the tile walk
 constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+// CTA pairs (cluster of two along M, tcgen05 cta_group::2): a pair computes a 256 x 256 tile per K block; each CTA
+// stages its 128 rows of A and HALF of the B rows (2 x 16 KiB per stage), so six stages fit and every byte of B
+// crosses the L2-to-SM fabric once per pair instead of once per CTA.
+constexpr int kPairStages = 6;
+constexpr int kPairBHalf = (kBN / 2) * kBK, kPairStageBytes = kATile + kPairBHalf;
+constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024 + 256;
+static_assert(kPairStages >= kStages, "the barrier arrays are sized for the pair kernel");
 constexpr int kTileFloats = kBM * kBN;
 
 struct GemmParams {
@@ -60,7 +67,7 @@ struct GemmParams {
 };
 
 struct Shared {
-    uint64_t full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], drain;
+    uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2], drain;
     uint32_t tmem_base;
     volatile uint32_t abort;
     volatile uint32_t last;
@@ -124,8 +131,9 @@ struct TileCoord {
     uint32_t m0, n0, tile, split, kb0, kb_count;
 };
 
-template <bool GATED>
-__device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t unit) {
+// With PAIR, `m_tiles` counts 256-row pair tiles and `rank` picks this CTA's 128 rows.
+template <bool GATED, bool PAIR = false>
+__device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t unit, uint32_t rank = 0) {
     TileCoord c;
     c.split = unit % p.splits;
     c.tile = unit / p.splits;
@@ -135,7 +143,7 @@ __device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t un
     const uint32_t band = c.tile / band_tiles, within = c.tile % band_tiles;
     const uint32_t band_rows = min((uint32_t)kBand, p.m_tiles - band * kBand);
     const uint32_t mt = band * kBand + within % band_rows, nt = within / band_rows;
-    c.m0 = mt * kBM;
+    c.m0 = PAIR ? mt * 2 * kBM + rank * kBM : mt * kBM;
     c.n0 = nt * (GATED ? kBN / 2 : kBN);
     const uint32_t base = p.kblocks / p.splits, extra = p.kblocks % p.splits;
     c.kb0 = c.split * base + min(c.split, extra);
@@ -228,25 +236,34 @@ __device__ __forceinline__ void write_row_any(const GemmParams& p, const float2 
 }
 
 // SPLIT instances carry the split-K exchange; keeping it out of the others keeps their epilogue in registers.
-template <bool GATED, bool SPLIT, int ACT>
+// PAIR instances run as clusters of two CTAs (launch with cluster dimension 2): CTA rank 0 is the leader, whose MMA
+// thread issues cta_group::2 MMAs for both and whose `full`/`tmem_empty` barriers collect both CTAs' arrivals; the
+// `empty`/`tmem_full` barriers of each CTA are signalled by the leader's commits.
+template <bool GATED, bool SPLIT, int ACT, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ CUtensorMap map_u, const GemmParams p) {
+    static_assert(!(PAIR && SPLIT), "split K runs on single CTAs");
+    constexpr uint32_t kStageCount = PAIR ? kPairStages : kStages;
+    constexpr uint32_t kStageSize = PAIR ? kPairStageBytes : kStageBytes;
     extern __shared__ uint8_t smem_raw[];
-    // The swizzled tiles need 1024-byte alignment; the dynamic shared memory base only promises 16.
+    // The swizzled tiles need 1024-byte alignment; the dynamic shared memory base only promises 16. (The offset is
+    // the same in both CTAs of a pair, which the pair MMA relies on.)
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Shared* sh = reinterpret_cast<Shared*>(tiles + (size_t)kStages * kStageBytes);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + (size_t)kStageCount * kStageSize);
     const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const uint32_t tiles_addr = ptx::smem_addr(tiles);
+    const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;
+    const uint32_t first_unit = PAIR ? blockIdx.x / 2 : blockIdx.x, unit_step = PAIR ? gridDim.x / 2 : gridDim.x;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (uint32_t s = 0; s < kStageCount; ++s) {
             ptx::mbar_init(ptx::smem_addr(&sh->full[s]), 1);
             ptx::mbar_init(ptx::smem_addr(&sh->empty[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_addr(&sh->tmem_full[b]), 1);
-            ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), kEpilogueThreads / 32);
+            ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), (PAIR ? 2 : 1) * kEpilogueThreads / 32);
         }
         ptx::mbar_init(ptx::smem_addr(&sh->drain), 1);
         sh->abort = 0;
@@ -259,11 +276,17 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (GATED) ptx::prefetch_tensormap(&map_u);
     }
     if (warp == kMmaWarp) {
-        ptx::tmem_alloc(ptx::smem_addr(&sh->tmem_base), kTmemColumns);
-        ptx::tmem_relinquish();
+        if (PAIR) {
+            ptx::tmem_alloc_pair(ptx::smem_addr(&sh->tmem_base), kTmemColumns);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_addr(&sh->tmem_base), kTmemColumns);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before();
-    __syncthreads();
+    if (PAIR) ptx::cluster_sync();  // the peer's barriers must exist before anything arrives on them
+    else __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
 
@@ -273,29 +296,45 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
-                const TileCoord c = unit_coord<GATED>(p, unit);
+            for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
+                const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
                 for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
-                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    const uint32_t stage = it % kStageCount, phase = (it / kStageCount) & 1u;
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->empty[stage]), phase ^ 1u, p, kRoleProducer, stage))) break;
                     const uint32_t full = ptx::smem_addr(&sh->full[stage]);
-                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const uint32_t base = tiles_addr + stage * kStageSize;
                     const int32_t x = (int32_t)((c.kb0 + i) * kBK);
-                    ptx::mbar_arrive_expect_tx(full, kStageBytes);
-                    ptx::tma_load_2d(base, &map_a, x, (int32_t)c.m0, full);
+                    if constexpr (PAIR) {
+                        // Both CTAs credit the leader's barrier; the leader expects the bytes of both.
+                        const uint32_t leader_full = ptx::map_to_rank(full, 0);
+                        if (rank == 0) ptx::mbar_arrive_expect_tx(full, 2 * kPairStageBytes);
+                        ptx::tma_load_2d_pair(base, &map_a, x, (int32_t)c.m0, leader_full);
 #pragma unroll
-                    for (int box = 0; box < kBN / kBoxRows; ++box) {
-                        const CUtensorMap* map = GATED && (box & 1) ? &map_u : &map_b;
-                        const int32_t y = (int32_t)(c.n0 + (GATED ? (box >> 1) : box) * kBoxRows);
-                        ptx::tma_load_2d(base + kATile + box * kBoxRows * kBK, map, x, y, full);
+                        for (int box = 0; box < 2; ++box) {
+                            // This CTA's half of the B rows: boxes 2*rank and 2*rank+1 of the four 64-row boxes.
+                            const CUtensorMap* map = GATED && box ? &map_u : &map_b;
+                            const int32_t y = (int32_t)(c.n0 + (GATED ? rank : 2 * rank + box) * kBoxRows);
+                            ptx::tma_load_2d_pair(base + kATile + box * kBoxRows * kBK, map, x, y, leader_full);
+                        }
+                    } else {
+                        ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                        ptx::tma_load_2d(base, &map_a, x, (int32_t)c.m0, full);
+#pragma unroll
+                        for (int box = 0; box < kBN / kBoxRows; ++box) {
+                            const CUtensorMap* map = GATED && (box & 1) ? &map_u : &map_b;
+                            const int32_t y = (int32_t)(c.n0 + (GATED ? (box >> 1) : box) * kBoxRows);
+                            ptx::tma_load_2d(base + kATile + box * kBoxRows * kBK, map, x, y, full);
+                        }
                     }
                 }
             }
             if (!ok) {
                 // Leave only after the copies already in flight have landed (bounded), so that none arrives in
                 // shared memory that no longer belongs to this block.
-                for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
-                    const uint32_t j = it - back, stage = j % kStages, phase = (j / kStages) & 1u;
+                // (A non-leader CTA of a pair has no barrier of its own to watch; its copies are bounded by the pair's
+                // final cluster barrier, which the leader reaches only after its own waits have ended.)
+                for (uint32_t back = 1; rank == 0 && back <= kStageCount && back <= it; ++back) {
+                    const uint32_t j = it - back, stage = j % kStageCount, phase = (j / kStageCount) & 1u;
                     for (uint32_t spin = 0; spin < 200000u; ++spin)
                         if (ptx::mbar_try_wait(ptx::smem_addr(&sh->full[stage]), phase)) break;
                 }
@@ -303,31 +342,40 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         __syncwarp();
       } else if (warp == kMmaWarp) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::idesc_e4m3(kBM, kBN);
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = ptx::idesc_e4m3(PAIR ? 2 * kBM : kBM, kBN);
             uint32_t it = 0;
             bool ok = true;
-            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
-                const TileCoord c = unit_coord<GATED>(p, unit);
+            for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
+                const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
                 for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
-                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    const uint32_t stage = it % kStageCount, phase = (it / kStageCount) & 1u;
                     const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_empty[buf]), use ^ 1u, p, kRoleMma, 16 + buf))) break;
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->full[stage]), phase, p, kRoleMma, stage))) break;
                     ptx::tc_fence_after();
-                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const uint32_t base = tiles_addr + stage * kStageSize;
                     const uint64_t desc_a = ptx::smem_desc_sw128(base), desc_b = ptx::smem_desc_sw128(base + kATile);
                     const uint32_t tmem_d = tmem_base + buf * kBN;
+                    if constexpr (PAIR) {
 #pragma unroll
-                    for (uint32_t k4 = 0; k4 < kBK / 32; ++k4)
-                        ptx::mma_f8(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, k4);
-                    ptx::mma_commit(ptx::smem_addr(&sh->empty[stage]));
-                    ptx::mma_commit(ptx::smem_addr(&sh->tmem_full[buf]));
+                        for (uint32_t k4 = 0; k4 < kBK / 32; ++k4)
+                            ptx::mma_f8_pair(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, k4);
+                        ptx::mma_commit_pair(ptx::smem_addr(&sh->empty[stage]), 3);
+                        ptx::mma_commit_pair(ptx::smem_addr(&sh->tmem_full[buf]), 3);
+                    } else {
+#pragma unroll
+                        for (uint32_t k4 = 0; k4 < kBK / 32; ++k4)
+                            ptx::mma_f8(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, k4);
+                        ptx::mma_commit(ptx::smem_addr(&sh->empty[stage]));
+                        ptx::mma_commit(ptx::smem_addr(&sh->tmem_full[buf]));
+                    }
                 }
             }
             if (!ok && it > 0) {
                 // Let the tensor core finish what was issued before the tensor memory goes back (bounded).
-                ptx::mma_commit(ptx::smem_addr(&sh->drain));
+                if (PAIR) ptx::mma_commit_pair(ptx::smem_addr(&sh->drain), 1);
+                else ptx::mma_commit(ptx::smem_addr(&sh->drain));
                 for (uint32_t spin = 0; spin < 200000u; ++spin)
                     if (ptx::mbar_try_wait(ptx::smem_addr(&sh->drain), 0)) break;
             }
@@ -341,8 +389,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const bool sa_e8m0 = p.e8m0_bits & 1u, sb_e8m0 = p.e8m0_bits & 2u, su_e8m0 = p.e8m0_bits & 4u;
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
-            const TileCoord c = unit_coord<GATED>(p, unit);
+        for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
+            const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
             const uint32_t row = c.m0 + lane_row;
             const bool row_live = row < p.m;
             const bool warp_live = c.m0 + quarter * 32 < p.m;
@@ -391,7 +439,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     ptx::tmem_wait_ld();
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+                    if (lane == 0) {
+                        // The MMA thread that reuses the buffer sits in the leader CTA of a pair.
+                        if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_addr(&sh->tmem_empty[buf]), 0));
+                        else ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+                    }
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[32 + j] = __ffma2_rn(make_float2(__uint_as_float(even[2 * j]), __uint_as_float(even[2 * j + 1])), f1x2, acc[32 + j]);
@@ -401,7 +453,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 } else {
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+                    if (lane == 0) {
+                        // The MMA thread that reuses the buffer sits in the leader CTA of a pair.
+                        if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_addr(&sh->tmem_empty[buf]), 0));
+                        else ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+                    }
                 }
             }
             if (!ok) break;
@@ -447,10 +503,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
     }
     ptx::tc_fence_before();
-    __syncthreads();
+    // A CTA of a pair must not leave while its peer may still read its tiles or signal its barriers.
+    if (PAIR) ptx::cluster_sync();
+    else __syncthreads();
     if (warp == kMmaWarp) {
         ptx::tc_fence_after();
-        ptx::tmem_dealloc(tmem_base, kTmemColumns);
+        if (PAIR) ptx::tmem_dealloc_pair(tmem_base, kTmemColumns);
+        else ptx::tmem_dealloc(tmem_base, kTmemColumns);
     }
 }
 
@@ -510,9 +569,20 @@ static int tensor_map_of(const void* base, uint64_t rows, uint64_t k, uint64_t s
 
 typedef void (*GemmKernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
 
+template <bool PAIR>
+static GemmKernel plain_kernel_for(bool gated, int activation) {
+    switch (activation) {
+        case ZCK_ACT_SILU: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_SILU, PAIR> : fp8_gemm_kernel<false, false, ZCK_ACT_SILU, PAIR>;
+        case ZCK_ACT_GELU_TANH: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_GELU_TANH, PAIR> : fp8_gemm_kernel<false, false, ZCK_ACT_GELU_TANH, PAIR>;
+        case ZCK_ACT_GELU: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_GELU, PAIR> : fp8_gemm_kernel<false, false, ZCK_ACT_GELU, PAIR>;
+        default: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_NONE, PAIR> : fp8_gemm_kernel<false, false, ZCK_ACT_NONE, PAIR>;
+    }
+}
+
 // Kernel instance for a launch: the activation is a compile-time constant except in the split-K instances.
-static GemmKernel kernel_for(bool gated, bool split, int activation) {
+static GemmKernel kernel_for(bool gated, bool split, int activation, bool pair = false) {
     if (split) return gated ? fp8_gemm_kernel<true, true, kActAny> : fp8_gemm_kernel<false, true, kActAny>;
+    if (pair) return plain_kernel_for<true>(gated, activation);
     switch (activation) {
         case ZCK_ACT_SILU: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_SILU> : fp8_gemm_kernel<false, false, ZCK_ACT_SILU>;
         case ZCK_ACT_GELU_TANH: return gated ? fp8_gemm_kernel<true, false, ZCK_ACT_GELU_TANH> : fp8_gemm_kernel<false, false, ZCK_ACT_GELU_TANH>;
@@ -524,9 +594,12 @@ static GemmKernel kernel_for(bool gated, bool split, int activation) {
 static int raise_shared_memory_limits() {
     for (int gated = 0; gated < 2; ++gated) {
         ZCK_CUDA(cudaFuncSetAttribute(kernel_for(gated, true, 0), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        for (int activation = ZCK_ACT_NONE; activation <= ZCK_ACT_GELU; ++activation)
+        for (int activation = ZCK_ACT_NONE; activation <= ZCK_ACT_GELU; ++activation) {
             ZCK_CUDA(cudaFuncSetAttribute(kernel_for(gated, false, activation), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kSmemBytes));
+            ZCK_CUDA(cudaFuncSetAttribute(kernel_for(gated, false, activation, true),
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kPairSmemBytes));
+        }
     }
     return ZCK_OK;
 }
@@ -571,6 +644,15 @@ static uint32_t choose_splits(uint32_t tiles, uint32_t kblocks, int sm_count) {
     uint32_t by_sms = (uint32_t)sm_count / tiles, by_depth = kblocks / 4;
     uint32_t splits = min(by_sms, by_depth);
     return splits < 1 ? 1 : splits;
+}
+
+// CTA pairs serve every unsplit product taller than one 128-row tile (ZCK_GEMM_PAIRS=0 turns them off).
+static bool use_pairs(const ZckGemmSizes& s, uint32_t splits) {
+    static int enabled = [] {
+        const char* text = getenv("ZCK_GEMM_PAIRS");
+        return text ? atoi(text) : 1;
+    }();
+    return enabled != 0 && splits == 1 && s.m > (uint32_t)kBM;
 }
 
 static int check_sizes(const ZckGemmSizes* s) {
@@ -635,6 +717,25 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
 
     dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if (use_pairs(*s, p.splits)) {
+        // Pair tiles are 256 rows tall; the unit count and the tile walk are in pair tiles.
+        p.m_tiles = (s->m + 2 * kBM - 1) / (2 * kBM);
+        p.units = p.m_tiles * p.n_tiles;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(2 * min(p.units, (uint32_t)state->sm_count / 2));
+        config.blockDim = threads;
+        config.dynamicSmemBytes = kPairSmemBytes;
+        config.stream = cs;
+        cudaLaunchAttribute cluster;
+        cluster.id = cudaLaunchAttributeClusterDimension;
+        cluster.val.clusterDim.x = 2;
+        cluster.val.clusterDim.y = 1;
+        cluster.val.clusterDim.z = 1;
+        config.attrs = &cluster;
+        config.numAttrs = 1;
+        ZCK_CUDA(cudaLaunchKernelEx(&config, kernel_for(gated, false, p.activation, true), map_a, map_b, map_u, p));
+        return ZCK_OK;
+    }
     kernel_for(gated, p.splits > 1, p.activation)<<<grid, threads, kSmemBytes, cs>>>(map_a, map_b, map_u, p);
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
