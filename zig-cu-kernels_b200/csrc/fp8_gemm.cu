@@ -38,13 +38,14 @@ static_assert((kLaunchRegs - kIdleRegs) * 128 >= (kEpilogueRegs - kLaunchRegs) *
               "the epilogue warpgroups would wait forever for registers");
 constexpr uint32_t kTmemColumns = 512;
 constexpr int kBand = 16;  // M tiles that share a band of the tile walk
-constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr size_t kControlBytes = 18 * 1024;  // barriers and staged scales (struct Shared)
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + kControlBytes;
 // CTA pairs (cluster of two along M, tcgen05 cta_group::2): a pair computes a 256 x 256 tile per K block; each CTA
 // stages its 128 rows of A and HALF of the B rows (2 x 16 KiB per stage), so six stages fit and every byte of B
 // crosses the L2-to-SM fabric once per pair instead of once per CTA.
 constexpr int kPairStages = 6;
 constexpr int kPairBHalf = (kBN / 2) * kBK, kPairStageBytes = kATile + kPairBHalf;
-constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024 + 256;
+constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024 + kControlBytes;
 static_assert(kPairStages >= kStages, "the barrier arrays are sized for the pair kernel");
 constexpr int kTileFloats = kBM * kBN;
 
@@ -66,12 +67,22 @@ struct GemmParams {
     uint32_t m_tiles, n_tiles, kblocks, splits, units;
 };
 
+// Scale staging: the epilogue threads copy the block scales of kScaleChunk K blocks at a time into shared memory
+// (cp.async, two chunks in flight), because a scale load that is consumed one K block later still stalls the drain
+// while the L2 is saturated by the tile traffic.
+constexpr int kScaleChunk = 8;
+
 struct Shared {
     uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2], drain;
     uint32_t tmem_base;
     volatile uint32_t abort;
     volatile uint32_t last;
+    float scale_a[2][kScaleChunk][kEpilogueThreads];           // [buffer][K block of the chunk][thread]: own row's scale
+    float scale_w[kEpilogueThreads / 32][2][2][kScaleChunk];   // [warp][buffer][weight (b|gate, up)][K block]
 };
+
+static_assert(sizeof(Shared) <= kControlBytes, "struct Shared outgrew its shared-memory budget");
+static_assert(kPairSmemBytes <= 227 * 1024 && kSmemBytes <= 227 * 1024, "over the shared memory of one CTA");
 
 enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2 };
 
@@ -107,6 +118,21 @@ __device__ __forceinline__ float load_scale(const void* base, uint64_t index, bo
     if (e8m0) return e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
     return static_cast<const float*>(base)[index];
 }
+
+// One scale value into shared memory without a register round trip when it is FP32 (4-byte cp.async); E8M0 bytes
+// are loaded, decoded and stored.
+__device__ __forceinline__ void stage_scale(float* dst, const void* base, uint64_t index, bool e8m0) {
+    if (e8m0) {
+        *dst = e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_addr(dst)),
+                     "l"(static_cast<const float*>(base) + index)
+                     : "memory");
+    }
+}
+__device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
 
 // The activations return what PyTorch's BF16 CUDA kernels return for the same BF16 input: same expressions in FP32,
 // same libdevice functions, default contraction. The result is rounded to BF16 by the caller.
@@ -400,21 +426,51 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             float2 acc[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
-            // Scales are fetched one K block ahead, so that no load sits between a full buffer and its drain.
+            // Scales come through shared memory, two chunks of kScaleChunk K blocks ahead of their use. Every thread
+            // stages the scale of its own row; lanes 0-7 (8-15) of each warp stage the weight (up) scales of the
+            // warp, which the other lanes read after a warp barrier.
             const uint64_t sa_base = (uint64_t)row * p.sa_row, sb_base = (uint64_t)scale_tile * p.sb_row,
                            su_base = (uint64_t)scale_tile * p.su_row;
-            float sa_next = row_live ? load_scale(p.scale_a, sa_base + (uint64_t)c.kb0 * p.sa_blk, sa_e8m0) : 0.0f;
-            float sb_next = load_scale(p.scale_b, sb_base + (uint64_t)c.kb0 * p.sb_blk, sb_e8m0);
-            float su_next = GATED ? load_scale(p.scale_u, su_base + (uint64_t)c.kb0 * p.su_blk, su_e8m0) : 0.0f;
+            const uint32_t chunks = (c.kb_count + kScaleChunk - 1) / kScaleChunk;
+            auto stage_chunk = [&](uint32_t chunk) {
+                if (chunk < chunks) {
+                    const uint32_t first = chunk * kScaleChunk, buffer = chunk & 1u;
+                    if (row_live) {
+#pragma unroll
+                        for (uint32_t j = 0; j < (uint32_t)kScaleChunk; ++j)
+                            if (first + j < c.kb_count)
+                                stage_scale(&sh->scale_a[buffer][j][threadIdx.x], p.scale_a,
+                                            sa_base + (uint64_t)(c.kb0 + first + j) * p.sa_blk, sa_e8m0);
+                    }
+                    const uint32_t j = lane % kScaleChunk;
+                    if (first + j < c.kb_count) {
+                        if (lane < (uint32_t)kScaleChunk)
+                            stage_scale(&sh->scale_w[warp][buffer][0][j], p.scale_b,
+                                        sb_base + (uint64_t)(c.kb0 + first + j) * p.sb_blk, sb_e8m0);
+                        else if (GATED && lane < 2u * kScaleChunk)
+                            stage_scale(&sh->scale_w[warp][buffer][1][j], p.scale_u,
+                                        su_base + (uint64_t)(c.kb0 + first + j) * p.su_blk, su_e8m0);
+                    }
+                }
+                stage_commit();  // an empty group keeps the group count in step with the chunk count
+            };
+            __syncwarp();  // the previous unit's reads of the weight scales are over
+            stage_chunk(0);
+            stage_chunk(1);
             for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
                 const uint32_t kb = c.kb0 + i;
                 const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
-                const float f0 = __fmul_rn(sa_next, sb_next);
-                const float f1 = GATED ? __fmul_rn(sa_next, su_next) : f0;
-                if (i + 1 < c.kb_count) {
-                    if (row_live) sa_next = load_scale(p.scale_a, sa_base + (uint64_t)(kb + 1) * p.sa_blk, sa_e8m0);
-                    sb_next = load_scale(p.scale_b, sb_base + (uint64_t)(kb + 1) * p.sb_blk, sb_e8m0);
-                    if (GATED) su_next = load_scale(p.scale_u, su_base + (uint64_t)(kb + 1) * p.su_blk, su_e8m0);
+                const uint32_t chunk = i / kScaleChunk, j = i % kScaleChunk;
+                if (j == 0) {
+                    stage_wait<1>();  // everything but the newest chunk has landed
+                    __syncwarp();
+                }
+                const float sa = sh->scale_a[chunk & 1u][j][threadIdx.x];
+                const float f0 = __fmul_rn(sa, sh->scale_w[warp][chunk & 1u][0][j]);
+                const float f1 = GATED ? __fmul_rn(sa, sh->scale_w[warp][chunk & 1u][1][j]) : f0;
+                if (j == kScaleChunk - 1 || i + 1 == c.kb_count) {
+                    __syncwarp();  // every lane has read this chunk's weight scales before its buffer is refilled
+                    if (j == kScaleChunk - 1) stage_chunk(chunk + 2);
                 }
                 if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, kb))) break;
                 ptx::tc_fence_after();
@@ -655,6 +711,23 @@ static bool use_pairs(const ZckGemmSizes& s, uint32_t splits) {
     return enabled != 0 && splits == 1 && s.m > (uint32_t)kBM;
 }
 
+// How many CTA pairs of the pair kernel the device runs at the same time (cached per device).
+static int resident_pairs(int device, int sm_count, cudaLaunchConfig_t config, GemmKernel kernel) {
+    static int cached[kMaxDevices] = {};
+    if (cached[device] > 0) return cached[device];
+    int clusters = 0;
+    config.gridDim = dim3((unsigned)sm_count);
+    cudaError_t error = cudaOccupancyMaxActiveClusters(&clusters, kernel, &config);
+    if (error != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        clusters = sm_count / 2;
+    }
+    if (const char* text = getenv("ZCK_GEMM_PAIR_COUNT")) clusters = max(1, atoi(text));
+    if (getenv("ZCK_VERBOSE")) fprintf(stderr, "zck: %d CTA pairs resident on device %d (%d SMs)\n", clusters, device, sm_count);
+    cached[device] = clusters;
+    return clusters;
+}
+
 static int check_sizes(const ZckGemmSizes* s) {
     ZCK_REQUIRE(s != nullptr, "sizes is NULL");
     ZCK_REQUIRE(s->k > 0 && s->k % kBK == 0, "block128 scaling needs a positive k %% 128 == 0, got %u", s->k);
@@ -722,7 +795,6 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
         p.m_tiles = (s->m + 2 * kBM - 1) / (2 * kBM);
         p.units = p.m_tiles * p.n_tiles;
         cudaLaunchConfig_t config = {};
-        config.gridDim = dim3(2 * min(p.units, (uint32_t)state->sm_count / 2));
         config.blockDim = threads;
         config.dynamicSmemBytes = kPairSmemBytes;
         config.stream = cs;
@@ -733,6 +805,10 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
         cluster.val.clusterDim.z = 1;
         config.attrs = &cluster;
         config.numAttrs = 1;
+        // The kernel is persistent: it must not launch more pairs than the device keeps resident at once, or the
+        // surplus pairs would only start when the first ones are done.
+        int resident = resident_pairs(device, state->sm_count, config, kernel_for(gated, false, p.activation, true));
+        config.gridDim = dim3(2 * min(p.units, (uint32_t)resident));
         ZCK_CUDA(cudaLaunchKernelEx(&config, kernel_for(gated, false, p.activation, true), map_a, map_b, map_u, p));
         return ZCK_OK;
     }

@@ -146,9 +146,10 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on an mbarrier that may live in another CTA of the cluster (`bar` from map_to_rank).
+// Arrive on an mbarrier that may live in another CTA of the cluster (`bar` from map_to_rank). Default semantics
+// (release at CTA scope): a cluster-scope release would wait for this thread's global loads in flight.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Tile load of one CTA of a pair into its own shared memory; the byte count is credited to `bar`, which may be the
 // barrier of the pair's leader CTA (`bar` from map_to_rank). Every CTA fetches its own tiles.
