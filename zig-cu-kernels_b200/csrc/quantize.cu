@@ -49,52 +49,75 @@ template <typename T, bool E8M0>
 __device__ __forceinline__ uint2 octet_codes(const Octet<T>& o, const GroupDivider& divide) {
     float q[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = E8M0 ? __fmul_rn(o.get(i), divide.scale) : divide(o.get(i));
+    for (int i = 0; i < 8; i += 2) {
+        if (E8M0) {
+            q[i] = __fmul_rn(o.get(i), divide.scale);
+            q[i + 1] = __fmul_rn(o.get(i + 1), divide.scale);
+        } else {
+            const float2 two = divide.pair(o.get(i), o.get(i + 1));
+            q[i] = two.x;
+            q[i + 1] = two.y;
+        }
+    }
     return make_uint2(e4m3x4_of(q[0], q[1], q[2], q[3]), e4m3x4_of(q[4], q[5], q[6], q[7]));
 }
 
 // ---------------------------------------------------------------------------------------------------------------
 // Rows: 8 lanes per scale group, each lane two octets (octet c*8+lane, so every load instruction is contiguous
-// over the 8 lanes). One group slot per 8 threads; groups are numbered row-major (row * groups_per_row + g).
+// over the 8 lanes). Groups are numbered row-major (row * groups_per_row + g). The grid is persistent: a block walks
+// group slots with the grid stride and has the loads of its NEXT slot in flight while it reduces, divides and stores
+// the current one, so every SM keeps a steady stream of 16-byte loads going.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kRowsThreads = 256;
+constexpr int kRowsSlotsPerBlock = kRowsThreads / 8;
 
-template <typename T, bool E8M0>
+template <typename T, bool E8M0, typename Index>
 __global__ void __launch_bounds__(kRowsThreads)
 quantize_rows_kernel(const T* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ codes, void* __restrict__ scales,
                      uint64_t scale_stride, uint32_t m, uint32_t groups_per_row) {
-    const uint64_t slot = (uint64_t)blockIdx.x * (kRowsThreads / 8) + threadIdx.x / 8;
     const uint32_t lane = threadIdx.x & 7;
-    const uint64_t total = (uint64_t)m * groups_per_row;
-    const bool live = slot < total;
-    const uint32_t row = live ? (uint32_t)(slot / groups_per_row) : 0;
-    const uint32_t g = live ? (uint32_t)(slot % groups_per_row) : 0;
-    const T* source = x + (uint64_t)row * x_stride + (uint64_t)g * kGroup;
-    Octet<T> o0, o1;
-    if (live) {
-        o0.load(source + 8 * lane);
-        o1.load(source + 8 * (8 + lane));
-    } else {
-        o0.zero();
-        o1.zero();
-    }
-    float amax = octet_amax(o1, octet_amax(o0, 0.0f));
-    amax = max_nan_over_lanes<8>(amax);  // all 32 lanes take part; the xor masks 4,2,1 stay inside each group of 8
-    float operand;
-    if (E8M0) {
-        uint32_t byte = scale_e8m0_of(amax);
-        operand = e8m0_reciprocal(byte);
-        if (live && lane == 0) static_cast<uint8_t*>(scales)[(uint64_t)g * scale_stride + row] = (uint8_t)byte;
-    } else {
-        operand = scale_f32_of(amax);
-        if (live && lane == 0) static_cast<float*>(scales)[(uint64_t)g * scale_stride + row] = operand;
-    }
-    if (live) {
-        // For E8M0 the "divider" only carries the power-of-two factor 2^(127-b) that multiplies every value.
-        const GroupDivider divide = GroupDivider::of(operand);
-        uint8_t* target = codes + ((uint64_t)row * groups_per_row + g) * kGroup;
-        st_global_v2(target + 8 * lane, octet_codes<T, E8M0>(o0, divide));
-        st_global_v2(target + 8 * (8 + lane), octet_codes<T, E8M0>(o1, divide));
+    const Index total = (Index)m * groups_per_row;
+    const Index stride = (Index)gridDim.x * kRowsSlotsPerBlock;
+    Index slot = (Index)blockIdx.x * kRowsSlotsPerBlock + threadIdx.x / 8;
+    // Every thread of a warp runs the same number of iterations (the shuffles need all 32 lanes): the trip count is
+    // taken from the first slot of the block, and slots past the end are dead.
+    const Index block_first = (Index)blockIdx.x * kRowsSlotsPerBlock;
+    Octet<T> next0, next1;
+    auto fetch = [&](Index at, Octet<T>& a, Octet<T>& b) {
+        if (at < total) {
+            const uint32_t row = (uint32_t)(at / groups_per_row), g = (uint32_t)(at % groups_per_row);
+            const T* source = x + (uint64_t)row * x_stride + (uint64_t)g * kGroup;
+            a.load(source + 8 * lane);
+            b.load(source + 8 * (8 + lane));
+        } else {
+            a.zero();
+            b.zero();
+        }
+    };
+    fetch(slot, next0, next1);
+    for (Index first = block_first; first < total; first += stride, slot += stride) {
+        const Octet<T> o0 = next0, o1 = next1;
+        fetch(slot + stride, next0, next1);
+        const bool live = slot < total;
+        const uint32_t row = live ? (uint32_t)(slot / groups_per_row) : 0, g = live ? (uint32_t)(slot % groups_per_row) : 0;
+        float amax = octet_amax(o1, octet_amax(o0, 0.0f));
+        amax = max_nan_over_lanes<8>(amax);  // the xor masks 4, 2, 1 stay inside each group of 8 lanes
+        float operand;
+        if (E8M0) {
+            uint32_t byte = scale_e8m0_of(amax);
+            operand = e8m0_reciprocal(byte);
+            if (live && lane == 0) static_cast<uint8_t*>(scales)[(uint64_t)g * scale_stride + row] = (uint8_t)byte;
+        } else {
+            operand = scale_f32_of(amax);
+            if (live && lane == 0) static_cast<float*>(scales)[(uint64_t)g * scale_stride + row] = operand;
+        }
+        if (live) {
+            // For E8M0 the "divider" only carries the power-of-two factor 2^(127-b) that multiplies every value.
+            const GroupDivider divide = GroupDivider::of(operand);
+            uint8_t* target = codes + ((uint64_t)row * groups_per_row + g) * kGroup;
+            st_global_v2(target + 8 * lane, octet_codes<T, E8M0>(o0, divide));
+            st_global_v2(target + 8 * (8 + lane), octet_codes<T, E8M0>(o1, divide));
+        }
     }
 }
 
@@ -171,24 +194,44 @@ extern "C" int zck_quantize_fp8_rows(const void* x, int x_kind, uint64_t x_strid
     if (m == 0 || k == 0) return ZCK_OK;
     int code = check_quantizer(x, x_kind, x_stride, codes, scales, scale_is_e8m0, m, k, "x");
     if (code != ZCK_OK) return code;
-    if (!device_state(device)) return ZCK_ERR_CUDA;
     DeviceGuard guard(device);
     ZCK_CUDA(guard.error);
+    DeviceState* state = device_state(device);
+    if (!state) return ZCK_ERR_CUDA;
     uint32_t groups_per_row = k / kGroup;
     uint64_t slots = (uint64_t)m * groups_per_row;
-    uint64_t blocks = (slots + kRowsThreads / 8 - 1) / (kRowsThreads / 8);
-    ZCK_REQUIRE(blocks <= 0x7FFFFFFFull, "x is too large: %llu blocks", (unsigned long long)blocks);
+    uint64_t needed = (slots + kRowsSlotsPerBlock - 1) / kRowsSlotsPerBlock;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    dim3 grid((unsigned)blocks), threads(kRowsThreads);
+    dim3 threads(kRowsThreads);
     uint8_t* q = static_cast<uint8_t*>(codes);
-#define ZCK_ROWS(T, E) \
-    quantize_rows_kernel<T, E><<<grid, threads, 0, s>>>(static_cast<const T*>(x), x_stride, q, scales, scale_stride, m, groups_per_row)
+    // 32-bit slot arithmetic (one division per slot) whenever the slot count and the grid stride allow it.
+    const bool narrow = slots + (uint64_t)state->sm_count * 8 * kRowsSlotsPerBlock < 0xFFFFFFFFull;
+    // The grid is persistent, so it holds exactly the blocks that are resident at once (asked of the runtime once per
+    // kernel instance).
+#define ZCK_ROWS_AS(T, E, I)                                                                                              \
+    do {                                                                                                                  \
+        static int per_sm = 0;                                                                                            \
+        if (per_sm == 0) {                                                                                                \
+            int blocks = 0;                                                                                               \
+            ZCK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, quantize_rows_kernel<T, E, I>, kRowsThreads, 0)); \
+            per_sm = blocks > 0 ? blocks : 1;                                                                             \
+        }                                                                                                                 \
+        uint64_t resident = (uint64_t)state->sm_count * per_sm;                                                           \
+        dim3 grid((unsigned)(needed < resident ? needed : resident));                                                     \
+        quantize_rows_kernel<T, E, I><<<grid, threads, 0, s>>>(static_cast<const T*>(x), x_stride, q, scales, scale_stride, m, groups_per_row); \
+    } while (0)
+#define ZCK_ROWS(T, E)                                   \
+    do {                                                 \
+        if (narrow) ZCK_ROWS_AS(T, E, uint32_t);         \
+        else ZCK_ROWS_AS(T, E, uint64_t);                \
+    } while (0)
     if (x_kind == ZCK_BF16) {
         if (scale_is_e8m0) ZCK_ROWS(__nv_bfloat16, true); else ZCK_ROWS(__nv_bfloat16, false);
     } else {
         if (scale_is_e8m0) ZCK_ROWS(float, true); else ZCK_ROWS(float, false);
     }
 #undef ZCK_ROWS
+#undef ZCK_ROWS_AS
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }

@@ -20,7 +20,8 @@ __device__ __forceinline__ float max_nan(float a, float b) {
     return d;
 }
 
-__device__ __forceinline__ float abs_f32(float a) { return __uint_as_float(__float_as_uint(a) & 0x7FFFFFFFu); }
+// fabsf (not a bit mask) so that the compiler can fold it into the operand of the max that follows.
+__device__ __forceinline__ float abs_f32(float a) { return fabsf(a); }
 
 template <int LANES>
 __device__ __forceinline__ float max_nan_over_lanes(float v) {
@@ -84,6 +85,19 @@ struct GroupDivider {
             return __uint_as_float((__float_as_uint(rounded) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
         }
         return __fdiv_rn(x, scale);
+    }
+    // Two quotients at once with the two-wide FP32 FMA (x * r as fma(x, r, -0), which keeps every sign).
+    __device__ __forceinline__ float2 pair(float x0, float x1) const {
+        if (fast) {
+            const float2 x = make_float2(x0, x1), r = make_float2(reciprocal, reciprocal);
+            const float2 q = __ffma2_rn(x, r, make_float2(-0.0f, -0.0f));
+            const float2 remainder = __ffma2_rn(q, make_float2(-scale, -scale), x);
+            const float2 rounded = __ffma2_rn(remainder, r, q);
+            return make_float2(
+                __uint_as_float((__float_as_uint(rounded.x) & 0x7FFFFFFFu) | (__float_as_uint(x0) & 0x80000000u)),
+                __uint_as_float((__float_as_uint(rounded.y) & 0x7FFFFFFFu) | (__float_as_uint(x1) & 0x80000000u)));
+        }
+        return make_float2(__fdiv_rn(x0, scale), __fdiv_rn(x1, scale));
     }
 };
 
