@@ -116,6 +116,19 @@ int zck_fp8_gated_gemm(const void* a, const void* w_gate, const void* w_up, cons
                        const void* bias_up, const void* residual, void* ws_parts, void* ws_counters,
                        const ZckGemmSizes* sizes, int device, void* stream);
 
+/* Replaces `run("gated", ...)` -> kernel `gemm_*_gated_*` of the BF16 GEMM
+ * (src/zig_cu_kernels/torch/gemm.py:196-216, src/zig_cu_kernels/gemm.py:495-531, zig/gemm_sm80.zig).
+ * a [m, k], w_gate and w_up [n, k] BF16 with one row stride; k % 8 == 0, n % 8 == 0. Only a_stride, b_stride,
+ * out_stride, residual_stride, m, n, k and activation of `sizes` are read.
+ * out = bf16(bf16(act(g)) * v) [+ residual], g = bf16(a w_gate^T + bias_gate), v = bf16(a w_up^T + bias_up). */
+int zck_gated_gemm_bf16(const void* a, const void* w_gate, const void* w_up, void* out, const void* bias_gate,
+                        const void* bias_up, const void* residual, const ZckGemmSizes* sizes, int device, void* stream);
+
+/* Replaces `run("store_bf16", ...)` of the BF16 GEMM (src/zig_cu_kernels/torch/gemm.py:120-153):
+ * out = bf16(act(bf16(a b^T + bias)) + residual), BF16 output only. */
+int zck_gemm_bf16(const void* a, const void* b, void* out, const void* bias, const void* residual,
+                  const ZckGemmSizes* sizes, int device, void* stream);
+
 /* No counterpart in the reference (its launchers always get their workspace from the caller's allocator).
  * zck_fp8_gemm for a host that must not allocate device memory: a program that calls this ABI straight from a
  * serving loop, with no caching allocator behind it. Such a host has typically given all free HBM to its own arena at

@@ -174,6 +174,24 @@ def fp8_gated_gemm(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate=Non
     return out.reshape(*lead, w_gate.shape[0])
 
 
+def gated_gemm_bf16(a, w_gate, w_up, bias_gate=None, bias_up=None, act="silu", residual=None):
+    """BF16 `gated_gemm`: exact (FP64) sums of BF16 products, then the BF16 rounding points.
+    tests/test_gemm.py:80-101 (`sums_of`, `biased`, `gated_reference`)."""
+    lead = a.shape[:-1]
+    flat = a.double().reshape(math.prod(lead), a.shape[-1])
+    s_gate, s_up = (flat @ w_gate.double().T).float(), (flat @ w_up.double().T).float()
+    out = gated_epilogue(s_gate, s_up, bias_gate, bias_up, act, None if residual is None else residual.reshape(s_gate.shape))
+    return out.reshape(*lead, w_gate.shape[0])
+
+
+def gemm_bf16(a, b, bias=None, act="none", residual=None):
+    """BF16 `gemm` with a BF16 output. tests/test_gemm.py:86-95 (`store_reference`)."""
+    lead = a.shape[:-1]
+    s = (a.double().reshape(math.prod(lead), a.shape[-1]) @ b.double().T).float()
+    out = store_epilogue(s, bias, act, None if residual is None else residual.reshape(s.shape))
+    return out.reshape(*lead, b.shape[0])
+
+
 def error_terms(a, scale_a, b, scale_b, gamma=2.0**-9):
     """Exact sums and the reference's allowed accumulation error gamma * sum(|A||B|) (subnormal E4M3 codes may count
     as zero). tests/test_fp8_gemm.py:147-162, :196-199."""

@@ -1,0 +1,78 @@
+"""BF16 `gated_gemm` / `gemm` on the GPU: bitwise on exact operands (multiples of 1/16, every partial sum exact in
+FP32; tests/test_gemm.py:60-62 of the reference), and within `delta + 2 ulp` of the exact-sum reference for random
+operands (README "Numerics and tolerances" there)."""
+
+import itertools
+
+import pytest
+import torch
+
+from helpers import BF16, assert_same_bits
+from oracle import rules
+
+pytestmark = pytest.mark.gpu
+ACTIVATIONS = ("none", "silu", "gelu_tanh", "gelu")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import zig_cu_kernels.torch as z
+    return z
+
+
+def exact_values(generator, *shape):
+    return (torch.randint(-8, 9, shape, device="cuda", generator=generator) / 16).bfloat16()
+
+
+@pytest.mark.parametrize("m,f,k", [(70, 264, 640), (1, 8, 8), (300, 520, 1000), (129, 136, 72), (2048, 1024, 512)])
+def test_exact_operands_are_bitwise(ops, m, f, k):
+    generator = torch.Generator(device="cuda").manual_seed(21)
+    a, gate, up = exact_values(generator, m, k), exact_values(generator, f, k), exact_values(generator, f, k)
+    bias, bias_up = (torch.randn(f, device="cuda", generator=generator).bfloat16() for _ in range(2))
+    residual = torch.randn(m, f, device="cuda", generator=generator).bfloat16()
+    for activation, with_bias, with_residual in itertools.product(ACTIVATIONS, (False, True), (False, True)):
+        b1, b2, r = (bias if with_bias else None), (bias_up if with_bias else None), (residual if with_residual else None)
+        out = ops.gated_gemm(a, gate, up, bias_gate=b1, bias_up=b2, activation=activation, residual=r)
+        assert_same_bits(out, rules.gated_gemm_bf16(a, gate, up, b1, b2, activation, r), f"gated {activation}")
+        out = ops.gemm(a, gate, bias=b1, activation=activation, residual=r)
+        assert_same_bits(out, rules.gemm_bf16(a, gate, b1, activation, r), f"gemm {activation}")
+
+
+def test_random_operands_stay_within_the_reference_bound(ops):
+    generator = torch.Generator(device="cuda").manual_seed(22)
+    for m, f, k in ((256, 512, 1024), (77, 136, 4096), (2, 37 * 8, 264)):
+        a = torch.randn(m, k, device="cuda", generator=generator).bfloat16()
+        gate = (torch.randn(f, k, device="cuda", generator=generator) * k**-0.5).bfloat16()
+        out = ops.gemm(a, gate)
+        exact = a.double() @ gate.double().T
+        magnitude = a.double().abs() @ gate.double().abs().T
+        rounds = -(-k // 16) + 1
+        delta = 2.0**-22 * rounds * magnitude
+        ulp = torch.exp2(torch.floor(torch.log2(exact.abs().clamp_min(2.0**-126))) - 7)
+        assert bool(((out.double() - exact).abs() <= delta + 2 * ulp).all())
+        up = (torch.randn(f, k, device="cuda", generator=generator) * k**-0.5).bfloat16()
+        gated = ops.gated_gemm(a, gate, up)
+        expected = rules.gated_gemm_bf16(a, gate, up)
+        error = (gated.double() - expected.double()).abs().max() / expected.double().abs().max()
+        assert float(error) <= 1e-2
+
+
+def test_layouts_and_errors(ops):
+    generator = torch.Generator(device="cuda").manual_seed(23)
+    m, f, k = 37, 136, 200
+    a, both = exact_values(generator, 2, m, k), exact_values(generator, 2 * f, k)
+    expected = rules.gated_gemm_bf16(a, both[:f], both[f:], act="silu")
+    out = ops.gated_gemm(a, both[:f], both[f:])
+    assert out.shape == (2, m, f)
+    assert_same_bits(out, expected, "halves of one weight, batched a")
+    residual = torch.randn(2, m, f, device="cuda", generator=generator).bfloat16()
+    buffer = residual.clone()
+    assert ops.gated_gemm(a, both[:f], both[f:], residual=buffer, out=buffer) is buffer
+    assert_same_bits(buffer, rules.gated_gemm_bf16(a, both[:f], both[f:], residual=residual), "residual is out")
+    assert ops.gated_gemm(a[:, :0], both[:f], both[f:]).shape == (2, 0, f)
+    with pytest.raises(ValueError, match="multiples of 8"):
+        ops.gated_gemm(a[..., :100], both[:f, :100], both[f:, :100])
+    with pytest.raises(ValueError, match="w_up must have the shape"):
+        ops.gated_gemm(a, both[:f], both[f:f + 8])
+    with pytest.raises(NotImplementedError):
+        ops.gemm(a, both[:f], out_dtype=torch.float32)

@@ -1,0 +1,256 @@
+// BF16 x BF16 GEMM with the gated (SwiGLU / GeGLU / bilinear) and plain epilogues, for sm_100a.
+//
+// Same skeleton as the FP8 kernel (persistent CTAs, TMA ring, tcgen05.mma into tensor memory, two epilogue
+// warpgroups), without block scales: the tensor core accumulates a whole tile over K in FP32 (kind::f16, four K=16
+// steps per 64-deep stage) and the epilogue drains a tile once, while the next tile already fills the other
+// tensor-memory buffer. Partial K blocks and partial tiles are zero-filled by the TMA unit.
+#include <cuda.h>
+
+#include "gemm_common.cuh"
+
+namespace zck {
+
+constexpr int kHalfBK = 64;  // BF16 elements per stage row: 128 bytes, the swizzle width
+
+// Instruction descriptor of kind::f16 with BF16 x BF16 -> FP32, both operands K-major, tile M x N.
+__host__ __device__ constexpr uint32_t idesc_bf16(uint32_t m, uint32_t n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <bool GATED, int ACT>
+__global__ void __launch_bounds__(kThreads, 1)
+bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_u, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Shared* sh = reinterpret_cast<Shared*>(tiles + (size_t)kStages * kStageBytes);
+    const uint32_t warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const uint32_t tiles_addr = ptx::smem_addr(tiles);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&sh->full[s]), 1);
+            ptx::mbar_init(ptx::smem_addr(&sh->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_addr(&sh->tmem_full[b]), 1);
+            ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), kEpilogueThreads / 32);
+        }
+        ptx::mbar_init(ptx::smem_addr(&sh->drain), 1);
+        sh->abort = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == kProducerWarp && lane == 0) {
+        ptx::prefetch_tensormap(&map_a);
+        ptx::prefetch_tensormap(&map_b);
+        if (GATED) ptx::prefetch_tensormap(&map_u);
+    }
+    if (warp == kMmaWarp) {
+        ptx::tmem_alloc(ptx::smem_addr(&sh->tmem_base), kTmemColumns);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp >= 8) {
+      ptx::reg_release<kIdleRegs>();
+      if (warp == kProducerWarp) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x) {
+                const TileCoord c = unit_coord<GATED>(p, unit);
+                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->empty[stage]), phase ^ 1u, p, kRoleProducer, stage))) break;
+                    const uint32_t full = ptx::smem_addr(&sh->full[stage]);
+                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const int32_t x = (int32_t)(i * kHalfBK);
+                    ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                    ptx::tma_load_2d(base, &map_a, x, (int32_t)c.m0, full);
+#pragma unroll
+                    for (int box = 0; box < kBN / kBoxRows; ++box) {
+                        const CUtensorMap* map = GATED && (box & 1) ? &map_u : &map_b;
+                        const int32_t y = (int32_t)(c.n0 + (GATED ? (box >> 1) : box) * kBoxRows);
+                        ptx::tma_load_2d(base + kATile + box * kBoxRows * kBK, map, x, y, full);
+                    }
+                }
+            }
+            if (!ok) {
+                for (uint32_t back = 1; back <= (uint32_t)kStages && back <= it; ++back) {
+                    const uint32_t j = it - back, stage = j % kStages, phase = (j / kStages) & 1u;
+                    for (uint32_t spin = 0; spin < 200000u; ++spin)
+                        if (ptx::mbar_try_wait(ptx::smem_addr(&sh->full[stage]), phase)) break;
+                }
+            }
+        }
+        __syncwarp();
+      } else if (warp == kMmaWarp) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16(kBM, kBN);
+            uint32_t it = 0, tile_count = 0;
+            bool ok = true;
+            for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x, ++tile_count) {
+                const TileCoord c = unit_coord<GATED>(p, unit);
+                const uint32_t buf = tile_count & 1u, use = (tile_count >> 1) & 1u;
+                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_empty[buf]), use ^ 1u, p, kRoleMma, 16 + buf))) break;
+                const uint32_t tmem_d = tmem_base + buf * kBN;
+                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                    const uint32_t stage = it % kStages, phase = (it / kStages) & 1u;
+                    if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->full[stage]), phase, p, kRoleMma, stage))) break;
+                    ptx::tc_fence_after();
+                    const uint32_t base = tiles_addr + stage * kStageBytes;
+                    const uint64_t desc_a = ptx::smem_desc_sw128(base), desc_b = ptx::smem_desc_sw128(base + kATile);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kHalfBK / 16; ++k4)
+                        mma_bf16(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, i | k4);
+                    ptx::mma_commit(ptx::smem_addr(&sh->empty[stage]));
+                }
+                if (ok) ptx::mma_commit(ptx::smem_addr(&sh->tmem_full[buf]));
+            }
+            if (!ok && it > 0) {
+                ptx::mma_commit(ptx::smem_addr(&sh->drain));
+                for (uint32_t spin = 0; spin < 200000u; ++spin)
+                    if (ptx::mbar_try_wait(ptx::smem_addr(&sh->drain), 0)) break;
+            }
+        }
+        __syncwarp();
+      }
+    } else {
+        ptx::reg_take<kEpilogueRegs>();
+        const uint32_t group = warp / 4, quarter = warp % 4;
+        const uint32_t lane_row = quarter * 32 + lane;
+        uint32_t tile_count = 0;
+        for (uint32_t unit = blockIdx.x; unit < p.units; unit += gridDim.x, ++tile_count) {
+            const TileCoord c = unit_coord<GATED>(p, unit);
+            const uint32_t row = c.m0 + lane_row;
+            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);
+            const uint32_t buf = tile_count & 1u, use = (tile_count >> 1) & 1u;
+            if (!wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, unit)) break;
+            ptx::tc_fence_after();
+            float2 acc[64];
+            const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + group * 128u;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                uint32_t even[32], odd[32];
+                ptx::tmem_ld_32x32(taddr + half * 64, even);
+                ptx::tmem_ld_32x32(taddr + half * 64 + 32, odd);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    acc[half * 32 + j] = make_float2(__uint_as_float(even[2 * j]), __uint_as_float(even[2 * j + 1]));
+                    acc[half * 32 + 16 + j] = make_float2(__uint_as_float(odd[2 * j]), __uint_as_float(odd[2 * j + 1]));
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+            if (row < p.m) write_row_any<GATED, ACT>(p, acc, row, col0);
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+typedef void (*Bf16Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+static Bf16Kernel bf16_kernel_for(bool gated, int activation) {
+    switch (activation) {
+        case ZCK_ACT_SILU: return gated ? bf16_gemm_kernel<true, ZCK_ACT_SILU> : bf16_gemm_kernel<false, ZCK_ACT_SILU>;
+        case ZCK_ACT_GELU_TANH: return gated ? bf16_gemm_kernel<true, ZCK_ACT_GELU_TANH> : bf16_gemm_kernel<false, ZCK_ACT_GELU_TANH>;
+        case ZCK_ACT_GELU: return gated ? bf16_gemm_kernel<true, ZCK_ACT_GELU> : bf16_gemm_kernel<false, ZCK_ACT_GELU>;
+        default: return gated ? bf16_gemm_kernel<true, ZCK_ACT_NONE> : bf16_gemm_kernel<false, ZCK_ACT_NONE>;
+    }
+}
+
+int init_bf16_gemm(int device) {
+    (void)device;
+    for (int gated = 0; gated < 2; ++gated)
+        for (int activation = ZCK_ACT_NONE; activation <= ZCK_ACT_GELU; ++activation)
+            ZCK_CUDA(cudaFuncSetAttribute(bf16_kernel_for(gated, activation), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)kSmemBytes));
+    return ZCK_OK;
+}
+
+static uint64_t bf16_wait_limit_ns() {
+    const char* text = getenv("ZCK_WAIT_LIMIT_NS");
+    uint64_t value = text ? strtoull(text, nullptr, 10) : 0;
+    return value ? value : 2000000000ull;
+}
+
+static int launch_bf16(bool gated, const void* a, const void* b, const void* u, void* out, const void* bias,
+                       const void* bias_u, const void* residual, const ZckGemmSizes* s, int device, void* stream) {
+    ZCK_REQUIRE(s != nullptr, "sizes is NULL");
+    ZCK_REQUIRE(s->k > 0 && s->k % 8 == 0 && s->n % 8 == 0, "k and n must be multiples of 8, got k = %u and n = %u", s->k, s->n);
+    ZCK_REQUIRE(s->activation >= ZCK_ACT_NONE && s->activation <= ZCK_ACT_GELU, "unknown activation %d", s->activation);
+    ZCK_REQUIRE(s->k <= 0x7FFFFF00u && s->m <= 0x7FFFFF00u && s->n <= 0x7FFFFF00u, "m, n or k is too large");
+    if (s->m == 0 || s->n == 0) return ZCK_OK;
+    ZCK_REQUIRE(a && b && out && (!gated || u), "an operand pointer is NULL");
+    ZCK_REQUIRE(aligned(a, 16) && aligned(b, 16) && (!gated || aligned(u, 16)), "a and the weights must start at a multiple of 16 bytes");
+    ZCK_REQUIRE((s->m <= 1 || (s->a_stride % 8 == 0 && s->a_stride >= s->k)) && (s->n <= 1 || (s->b_stride % 8 == 0 && s->b_stride >= s->k)),
+                "the row strides of a and the weights must be multiples of 16 bytes and at least k");
+    ZCK_REQUIRE(aligned(out, 16) && (s->m <= 1 || s->out_stride % 8 == 0), "out needs 16-byte aligned rows");
+    ZCK_REQUIRE(!residual || (aligned(residual, 16) && s->residual_stride % 8 == 0), "residual needs 16-byte aligned rows");
+    ZCK_REQUIRE((!bias || aligned(bias, 16)) && (!bias_u || aligned(bias_u, 16)), "the biases must start at a multiple of 16 bytes");
+    DeviceGuard guard(device);
+    ZCK_CUDA(guard.error);
+    DeviceState* state = device_state(device);
+    if (!state) return ZCK_ERR_CUDA;
+    GemmParams p = {};
+    p.bias = static_cast<const __nv_bfloat16*>(bias);
+    p.bias_u = static_cast<const __nv_bfloat16*>(bias_u);
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.out = static_cast<__nv_bfloat16*>(out);
+    p.status = state->status_device;
+    p.wait_ns = bf16_wait_limit_ns();
+    p.out_stride = s->out_stride;
+    p.residual_stride = s->residual_stride;
+    p.m = s->m; p.n = s->n; p.k = s->k; p.activation = s->activation;
+    p.m_tiles = (s->m + kBM - 1) / kBM;
+    p.n_tiles = (s->n + (gated ? kBN / 2 : kBN) - 1) / (gated ? kBN / 2 : kBN);
+    p.kblocks = (s->k + kHalfBK - 1) / kHalfBK;
+    p.splits = 1;
+    uint64_t units = (uint64_t)p.m_tiles * p.n_tiles;
+    ZCK_REQUIRE(units <= 0x7FFFFFFFull, "too many tiles");
+    p.units = (uint32_t)units;
+    CUtensorMap map_a, map_b, map_u;
+    int code;
+    if ((code = tensor_map_rows(a, s->m, s->k, s->a_stride, kBM, 2, device, &map_a)) != ZCK_OK) return code;
+    if ((code = tensor_map_rows(b, s->n, s->k, s->b_stride, kBoxRows, 2, device, &map_b)) != ZCK_OK) return code;
+    map_u = map_b;
+    if (gated && (code = tensor_map_rows(u, s->n, s->k, s->b_stride, kBoxRows, 2, device, &map_u)) != ZCK_OK) return code;
+    dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
+    bf16_kernel_for(gated, p.activation)<<<grid, threads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_u, p);
+    ZCK_CUDA(cudaGetLastError());
+    return ZCK_OK;
+}
+
+}  // namespace zck
+
+using namespace zck;
+
+extern "C" int zck_gated_gemm_bf16(const void* a, const void* w_gate, const void* w_up, void* out, const void* bias_gate,
+                                   const void* bias_up, const void* residual, const ZckGemmSizes* sizes, int device,
+                                   void* stream) {
+    return launch_bf16(true, a, w_gate, w_up, out, bias_gate, bias_up, residual, sizes, device, stream);
+}
+
+extern "C" int zck_gemm_bf16(const void* a, const void* b, void* out, const void* bias, const void* residual,
+                             const ZckGemmSizes* sizes, int device, void* stream) {
+    return launch_bf16(false, a, b, nullptr, out, bias, nullptr, residual, sizes, device, stream);
+}

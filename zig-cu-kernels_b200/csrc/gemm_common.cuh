@@ -1,0 +1,251 @@
+// Device code shared by the GEMM kernels of libzck_b200: tile constants, launch parameters, the shared-memory
+// control block, bounded barrier waits, the tile walk and the BF16 output phase.
+#pragma once
+
+#include <cuda.h>
+
+#include "sm100_ptx.cuh"
+#include "zck_device.cuh"
+#include "zck_host.h"
+
+namespace zck {
+
+constexpr int kBM = 128, kBN = 256, kBK = 128;
+constexpr int kStages = 4;
+constexpr int kATile = kBM * kBK, kBTile = kBN * kBK, kStageBytes = kATile + kBTile;
+constexpr int kBoxRows = 64;  // rows of one B box
+constexpr int kThreads = 384, kEpilogueThreads = 256;  // three warpgroups: two epilogue, one for the copy and MMA warps
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+// Register redistribution. The block starts at kLaunchRegs per thread (what ptxas grants 384 threads); the third
+// warpgroup drops to kIdleRegs and the two epilogue warpgroups rise to kEpilogueRegs. The rise BLOCKS until the
+// block's own pool holds enough released registers, so released must cover taken exactly or the kernel hangs.
+constexpr int kLaunchRegs = 168, kIdleRegs = 40, kEpilogueRegs = 232;
+static_assert((kLaunchRegs - kIdleRegs) * 128 >= (kEpilogueRegs - kLaunchRegs) * kEpilogueThreads,
+              "the epilogue warpgroups would wait forever for registers");
+constexpr uint32_t kTmemColumns = 512;
+constexpr int kBand = 16;  // M tiles that share a band of the tile walk
+constexpr size_t kControlBytes = 18 * 1024;  // barriers and staged scales (struct Shared)
+constexpr size_t kSmemBytes = (size_t)kStages * kStageBytes + 1024 /* alignment slack */ + kControlBytes;
+// CTA pairs (cluster of two along M, tcgen05 cta_group::2): a pair computes a 256 x 256 tile per K block; each CTA
+// stages its 128 rows of A and HALF of the B rows (2 x 16 KiB per stage), so six stages fit and every byte of B
+// crosses the L2-to-SM fabric once per pair instead of once per CTA.
+constexpr int kPairStages = 6;
+constexpr int kPairBHalf = (kBN / 2) * kBK, kPairStageBytes = kATile + kPairBHalf;
+constexpr size_t kPairSmemBytes = (size_t)kPairStages * kPairStageBytes + 1024 + kControlBytes;
+static_assert(kPairStages >= kStages, "the barrier arrays are sized for the pair kernel");
+constexpr int kTileFloats = kBM * kBN;
+
+struct GemmParams {
+    const void* scale_a;
+    const void* scale_b;
+    const void* scale_u;
+    const __nv_bfloat16* bias;
+    const __nv_bfloat16* bias_u;
+    const __nv_bfloat16* residual;
+    __nv_bfloat16* out;
+    float* parts;
+    uint32_t* counters;
+    uint32_t* status;
+    uint64_t wait_ns;
+    uint64_t sa_row, sa_blk, sb_row, sb_blk, su_row, su_blk, out_stride, residual_stride;
+    uint32_t m, n, k, e8m0_bits;
+    int32_t activation;
+    uint32_t m_tiles, n_tiles, kblocks, splits, units;
+};
+
+// Scale staging: the epilogue threads copy the block scales of kScaleChunk K blocks at a time into shared memory
+// (cp.async, two chunks in flight), because a scale load that is consumed one K block later still stalls the drain
+// while the L2 is saturated by the tile traffic.
+constexpr int kScaleChunk = 8;
+
+struct Shared {
+    uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2], drain;
+    uint32_t tmem_base;
+    volatile uint32_t abort;
+    volatile uint32_t last;
+    float scale_a[2][kScaleChunk][kEpilogueThreads];           // [buffer][K block of the chunk][thread]: own row's scale
+    float scale_w[kEpilogueThreads / 32][2][2][kScaleChunk];   // [warp][buffer][weight (b|gate, up)][K block]
+};
+
+static_assert(sizeof(Shared) <= kControlBytes, "struct Shared outgrew its shared-memory budget");
+static_assert(kPairSmemBytes <= 227 * 1024 && kSmemBytes <= 227 * 1024, "over the shared memory of one CTA");
+
+enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2 };
+
+// Bounded wait: gives up after `wait_ns` (or as soon as another role gave up), records who and where, and returns
+// false. Nothing traps; the block then leaves through the common exit.
+__device__ __forceinline__ bool wait_barrier(Shared* sh, uint32_t bar, uint32_t parity, const GemmParams& p, uint32_t role,
+                                             uint32_t where) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t start = ptx::global_timer();
+    for (uint32_t spin = 1;; ++spin) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((spin & 63u) == 0) {
+            if (sh->abort) return false;
+            if (ptx::global_timer() - start > p.wait_ns) {
+                sh->abort = 1;
+                // Plain stores to the host-mapped record: the first reporter wins approximately, which is all a
+                // diagnostic needs, and no atomic has to cross the bus.
+                volatile uint32_t* status = p.status;
+                if (status[0] == 0u) {
+                    status[1] = blockIdx.x;
+                    status[2] = where;
+                    status[0] = 1u + role;
+                }
+                status[3] = status[3] + 1u;
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ float load_scale(const void* base, uint64_t index, bool e8m0) {
+    if (e8m0) return e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
+    return static_cast<const float*>(base)[index];
+}
+
+// One scale value into shared memory without a register round trip when it is FP32 (4-byte cp.async); E8M0 bytes
+// are loaded, decoded and stored.
+__device__ __forceinline__ void stage_scale(float* dst, const void* base, uint64_t index, bool e8m0) {
+    if (e8m0) {
+        *dst = e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_addr(dst)),
+                     "l"(static_cast<const float*>(base) + index)
+                     : "memory");
+    }
+}
+__device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING>
+__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// The activations return what PyTorch's BF16 CUDA kernels return for the same BF16 input: same expressions in FP32,
+// same libdevice functions, default contraction. The result is rounded to BF16 by the caller.
+template <int ACT>
+__device__ __forceinline__ float activate(float x) {
+    if (ACT == ZCK_ACT_SILU) return x / (1.0f + expf(-x));
+    if (ACT == ZCK_ACT_GELU_TANH) {
+        constexpr float kBeta = (float)(1.41421356237309504880 * 1.12837916709551257390 * 0.5);
+        constexpr float kKappa = 0.044715f;
+        float x_cube = x * x * x;
+        float inner = kBeta * (x + kKappa * x_cube);
+        return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    if (ACT == ZCK_ACT_GELU) {
+        constexpr float kAlpha = (float)0.70710678118654752440;
+        return x * 0.5f * (1.0f + erff(x * kAlpha));
+    }
+    return x;
+}
+
+struct TileCoord {
+    uint32_t m0, n0, tile, split, kb0, kb_count;
+};
+
+// With PAIR, `m_tiles` counts 256-row pair tiles and `rank` picks this CTA's 128 rows.
+template <bool GATED, bool PAIR = false>
+__device__ __forceinline__ TileCoord unit_coord(const GemmParams& p, uint32_t unit, uint32_t rank = 0) {
+    TileCoord c;
+    c.split = unit % p.splits;
+    c.tile = unit / p.splits;
+    // Tile walk: bands of kBand M tiles; inside a band the M tile varies fastest, so neighbours share the B tile and
+    // the A tiles of a band stay in L2.
+    const uint32_t band_tiles = kBand * p.n_tiles;
+    const uint32_t band = c.tile / band_tiles, within = c.tile % band_tiles;
+    const uint32_t band_rows = min((uint32_t)kBand, p.m_tiles - band * kBand);
+    const uint32_t mt = band * kBand + within % band_rows, nt = within / band_rows;
+    c.m0 = PAIR ? mt * 2 * kBM + rank * kBM : mt * kBM;
+    c.n0 = nt * (GATED ? kBN / 2 : kBN);
+    const uint32_t base = p.kblocks / p.splits, extra = p.kblocks % p.splits;
+    c.kb0 = c.split * base + min(c.split, extra);
+    c.kb_count = base + (c.split < extra ? 1u : 0u);
+    return c;
+}
+
+// Output phase of one thread: 128 accumulators of row `row`. Store tiles: columns col0 .. col0+127. Gated tiles:
+// acc[0..63] are gate sums and acc[64..127] up sums of columns col0 .. col0+63.
+// Element `index` of the 128 accumulators, which live as 64 packed pairs (for the two-wide FP32 FMA).
+__device__ __forceinline__ float acc_at(const float2 (&acc)[64], int index) {
+    return (index & 1) ? acc[index >> 1].y : acc[index >> 1].x;
+}
+
+// Value `i` of eight BF16 values packed in a uint4.
+__device__ __forceinline__ float bf16_at(const uint4& w, int i) {
+    const uint32_t word = i < 2 ? w.x : i < 4 ? w.y : i < 6 ? w.z : w.w;
+    return (i & 1) ? bf16_hi(word) : bf16_lo(word);
+}
+
+template <bool GATED, int ACT>
+__device__ __forceinline__ void write_row(const GemmParams& p, const float2 (&acc)[64], uint32_t row, uint32_t col0) {
+    constexpr int kColumns = GATED ? 64 : 128;
+    __nv_bfloat16* out = p.out + (uint64_t)row * p.out_stride;
+    const __nv_bfloat16* residual = p.residual ? p.residual + (uint64_t)row * p.residual_stride : nullptr;
+#pragma unroll
+    for (int j = 0; j < kColumns; j += 8) {
+        const uint32_t col = col0 + j;
+        if (col >= p.n) break;  // n % 8 == 0: an octet is inside or outside as a whole
+        // Bias and residual octets either stay packed (four registers each, unpacked value by value) or are widened
+        // to FP32 up front. Which of the two keeps ptxas from spilling inside the K loop differs by instance and was
+        // chosen by measurement: packed for the gated tiles, widened for the store tiles.
+        float y[8];
+        if constexpr (GATED) {
+            uint4 bias = make_uint4(0, 0, 0, 0), bias_u = make_uint4(0, 0, 0, 0), res = make_uint4(0, 0, 0, 0);
+            if (p.bias) bias = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+            if (p.bias_u) bias_u = __ldg(reinterpret_cast<const uint4*>(p.bias_u + col));
+            if (residual) res = ld_global_v4(residual + col);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float t = bf16_round(__fadd_rn(acc_at(acc, j + i), bf16_at(bias, i)));
+                float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
+                float v = bf16_round(__fadd_rn(acc_at(acc, 64 + j + i), bf16_at(bias_u, i)));
+                u = bf16_round(__fmul_rn(u, v));
+                y[i] = residual ? __fadd_rn(u, bf16_at(res, i)) : u;
+            }
+        } else {
+            float wide_bias[8], wide_res[8];
+            if (p.bias) {
+                uint4 w = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+                wide_bias[0] = bf16_lo(w.x); wide_bias[1] = bf16_hi(w.x); wide_bias[2] = bf16_lo(w.y); wide_bias[3] = bf16_hi(w.y);
+                wide_bias[4] = bf16_lo(w.z); wide_bias[5] = bf16_hi(w.z); wide_bias[6] = bf16_lo(w.w); wide_bias[7] = bf16_hi(w.w);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) wide_bias[i] = 0.0f;
+            }
+            if (residual) {
+                uint4 w = ld_global_v4(residual + col);
+                wide_res[0] = bf16_lo(w.x); wide_res[1] = bf16_hi(w.x); wide_res[2] = bf16_lo(w.y); wide_res[3] = bf16_hi(w.y);
+                wide_res[4] = bf16_lo(w.z); wide_res[5] = bf16_hi(w.z); wide_res[6] = bf16_lo(w.w); wide_res[7] = bf16_hi(w.w);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float t = bf16_round(__fadd_rn(acc_at(acc, j + i), wide_bias[i]));
+                float u = ACT == ZCK_ACT_NONE ? t : bf16_round(activate<ACT>(t));
+                y[i] = residual ? __fadd_rn(u, wide_res[i]) : u;
+            }
+        }
+        st_global_v4(out + col, make_uint4(bf16x2_of(y[0], y[1]), bf16x2_of(y[2], y[3]), bf16x2_of(y[4], y[5]),
+                                           bf16x2_of(y[6], y[7])));
+    }
+}
+
+// ACT >= 0 names the activation at compile time (one output phase in the kernel: no spills); ACT < 0 picks at run
+// time (the split-K instances, which are bound by memory, not by registers).
+constexpr int kActAny = -1;
+
+template <bool GATED, int ACT>
+__device__ __forceinline__ void write_row_any(const GemmParams& p, const float2 (&acc)[64], uint32_t row, uint32_t col0) {
+    if constexpr (ACT >= 0) {
+        write_row<GATED, ACT>(p, acc, row, col0);
+        return;
+    }
+    switch (p.activation) {
+        case ZCK_ACT_SILU: write_row<GATED, ZCK_ACT_SILU>(p, acc, row, col0); break;
+        case ZCK_ACT_GELU_TANH: write_row<GATED, ZCK_ACT_GELU_TANH>(p, acc, row, col0); break;
+        case ZCK_ACT_GELU: write_row<GATED, ZCK_ACT_GELU>(p, acc, row, col0); break;
+        default: write_row<GATED, ZCK_ACT_NONE>(p, acc, row, col0); break;
+    }
+}
+
+
+}  // namespace zck

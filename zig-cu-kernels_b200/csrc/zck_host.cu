@@ -62,6 +62,7 @@ extern "C" int zck_init(int device) {
     state->status_device = static_cast<uint32_t*>(mapped);
     int code = init_gemm(device);
     if (code != ZCK_OK) return code;
+    if ((code = init_bf16_gemm(device)) != ZCK_OK) return code;
     state->ready = true;
     return ZCK_OK;
 }

@@ -10,6 +10,8 @@
 
 #include "../../include/zck.h"
 
+struct CUtensorMap_st;  // the driver's tensor map (cuda.h)
+
 namespace zck {
 
 constexpr int kMaxDevices = 64;
@@ -58,5 +60,11 @@ inline bool aligned(const void* p, uintptr_t bytes) { return (reinterpret_cast<u
 
 // Hooks each kernel file provides for zck_init (shared-memory opt-in and the like).
 int init_gemm(int device);
+int init_bf16_gemm(int device);
+
+// Cached TMA descriptor of a row-major matrix [rows, k] of 1- or 2-byte elements (k, stride in elements): boxes of
+// 128 bytes x box_rows, 128-byte swizzle, zero fill outside the matrix. Defined with the FP8 GEMM.
+int tensor_map_rows(const void* base, uint64_t rows, uint64_t k, uint64_t stride, uint32_t box_rows, int element_bytes,
+                    int device, ::CUtensorMap_st* out);
 
 }  // namespace zck

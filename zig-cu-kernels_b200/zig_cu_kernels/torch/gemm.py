@@ -1,0 +1,162 @@
+"""BF16 `gated_gemm` and `gemm` as PyTorch custom ops over libzck_b200 (tcgen05 `kind::f16` kernel).
+
+Schemas and rounding points of the reference's src/zig_cu_kernels/torch/gemm.py (`gemm` :120-167, `gated_gemm`
+:170-233): BF16 operands, FP32 accumulation, BF16 rounding after the bias, after the activation, after the gate
+product and after the residual, as PyTorch's BF16 CUDA ops do. `gemm` is built for BF16 outputs only.
+"""
+
+import ctypes
+import math
+
+import torch
+
+from .. import _lib
+from .common import need_below, need_choice, need_dtype, raw_stream, readable_rows, writable_rows
+from .fp8_gemm import ACTIVATIONS, address, bias_operand, output_target, residual_operand
+from .ops import Out, Param, define
+
+__all__ = ["gated_gemm", "gemm", "gated_gemm_op", "gated_gemm_out_op", "gemm_op", "gemm_out_op"]
+
+BF16 = torch.bfloat16
+LIMIT_31 = 1 << 31
+
+
+def check_product_sizes(a, columns, name):
+    k = a.shape[-1]
+    if k % 8 or columns % 8:
+        raise ValueError(f"k and {name} must be multiples of 8, got k = {k} and {name} = {columns}")
+    need_below(LIMIT_31, m=math.prod(a.shape[:-1]), k=k, **{name: columns})
+
+
+def sizes_of(a_stride, w_stride, target, residual_stride, m, n, k, activation):
+    return _lib.GemmSizes(a_stride=a_stride, b_stride=w_stride, out_stride=writable_rows(target),
+                          residual_stride=residual_stride, m=m, n=n, k=k, e8m0_bits=0,
+                          activation=_lib.ACTIVATIONS[activation], splits=1)
+
+
+# ---- gated_gemm ----------------------------------------------------------------------------------------------------
+
+def check_gated(a, w_gate, w_up, bias_gate, bias_up, residual, activation):
+    for name, tensor in (("a", a), ("w_gate", w_gate), ("w_up", w_up), ("bias_gate", bias_gate), ("bias_up", bias_up),
+                         ("residual", residual)):
+        need_dtype(name, tensor, (BF16,))
+    need_choice("activation", activation, ACTIVATIONS)
+    if a.dim() < 1 or w_gate.dim() != 2 or w_up.dim() != 2:
+        raise ValueError("a must be [..., k], and w_gate and w_up must be [f, k]")
+
+
+def check_gated_sizes(a, w_gate, w_up, bias_gate, bias_up, residual, activation):
+    f = w_gate.shape[0]
+    if w_gate.shape[1] != a.shape[-1]:
+        raise ValueError(f"w_gate must be [f, {a.shape[-1]}] for a of the shape {tuple(a.shape)}, got "
+                         f"{tuple(w_gate.shape)}")
+    if w_up.shape != w_gate.shape:
+        raise ValueError(f"w_up must have the shape {tuple(w_gate.shape)}, got {tuple(w_up.shape)}")
+    check_product_sizes(a, f, "f")
+    for name, bias in (("bias_gate", bias_gate), ("bias_up", bias_up)):
+        if bias is not None and tuple(bias.shape) != (f,):
+            raise ValueError(f"{name} must have the shape {(f,)}, got {tuple(bias.shape)}")
+    if residual is not None and tuple(residual.shape) != (*a.shape[:-1], f):
+        raise ValueError(f"residual must have the shape {(*a.shape[:-1], f)}, got {tuple(residual.shape)}")
+
+
+def gated_output(a, w_gate, w_up, bias_gate, bias_up, residual, activation):
+    return a.new_empty((*a.shape[:-1], w_gate.shape[0]), dtype=BF16)
+
+
+def gated_into(a, w_gate, w_up, bias_gate, bias_up, residual, activation, out):
+    lead, (f, k) = tuple(a.shape[:-1]), w_gate.shape
+    if tuple(out.shape) != (*lead, f):
+        raise ValueError(f"out must have the shape {(*lead, f)}, got {tuple(out.shape)}")
+    m = math.prod(lead)
+    if m == 0 or f == 0:
+        return
+    target = output_target(out, (a, w_gate, w_up, bias_gate, bias_up), residual)
+    a, a_stride = readable_rows(a)
+    (gate, gate_stride), (up, up_stride) = readable_rows(w_gate), readable_rows(w_up)
+    if gate_stride != up_stride and f > 1:
+        gate, up = gate.contiguous(), up.contiguous()
+        gate_stride = k
+    bias_gate, bias_up = bias_operand(bias_gate), bias_operand(bias_up)
+    residual, residual_stride = residual_operand(residual)
+    sizes = sizes_of(a_stride, gate_stride, target, residual_stride, m, f, k, activation)
+    device = a.get_device()
+    _lib.check(_lib.library().zck_gated_gemm_bf16(
+        a.data_ptr(), gate.data_ptr(), up.data_ptr(), target.data_ptr(), address(bias_gate), address(bias_up),
+        address(residual), ctypes.byref(sizes), device, raw_stream(device)))
+    if target is not out:
+        out.copy_(target)
+
+
+GATED_GEMM = define(
+    "gated_gemm",
+    params=[Param("Tensor", "a"), Param("Tensor", "w_gate"), Param("Tensor", "w_up"), Param("Tensor?", "bias_gate"),
+            Param("Tensor?", "bias_up"), Param("Tensor?", "residual"), Param("str", "activation")],
+    outs=[Out("out", "out", gated_output, BF16)], check=check_gated, check_sizes=check_gated_sizes, run=gated_into)
+gated_gemm_op, gated_gemm_out_op = GATED_GEMM.functional, GATED_GEMM.out
+
+
+def gated_gemm(a, w_gate, w_up, *, bias_gate=None, bias_up=None, activation="silu", residual=None, out=None):
+    """BF16 gated linear unit `bf16(bf16(act(g)) * v) [+ residual]` with `g = bf16(a w_gate^T + bias_gate)` and
+    `v = bf16(a w_up^T + bias_up)`; `w_gate`, `w_up` are `[f, k]` and may be the halves of one `[2f, k]` weight."""
+    return GATED_GEMM(a, w_gate, w_up, bias_gate, bias_up, residual, activation, outputs={"out": out})
+
+
+# ---- gemm ----------------------------------------------------------------------------------------------------------
+
+def check_gemm(a, b, bias, residual, activation, out_dtype):
+    for name, tensor in (("a", a), ("b", b), ("bias", bias), ("residual", residual)):
+        need_dtype(name, tensor, (BF16,))
+    need_choice("activation", activation, ACTIVATIONS)
+    need_choice("out_dtype", out_dtype, (BF16, torch.float32))
+    if out_dtype == torch.float32:
+        raise NotImplementedError("gemm with an FP32 output is not built in this library yet; only BF16 is")
+    if a.dim() < 1 or b.dim() != 2:
+        raise ValueError("a must be [..., k], and b must be [n, k]")
+
+
+def check_gemm_sizes(a, b, bias, residual, activation, out_dtype):
+    n = b.shape[0]
+    if b.shape[1] != a.shape[-1]:
+        raise ValueError(f"b must be [n, {a.shape[-1]}] for a of the shape {tuple(a.shape)}, got {tuple(b.shape)}")
+    check_product_sizes(a, n, "n")
+    if bias is not None and tuple(bias.shape) != (n,):
+        raise ValueError(f"bias must have the shape {(n,)}, got {tuple(bias.shape)}")
+    if residual is not None and tuple(residual.shape) != (*a.shape[:-1], n):
+        raise ValueError(f"residual must have the shape {(*a.shape[:-1], n)}, got {tuple(residual.shape)}")
+
+
+def gemm_output(a, b, bias, residual, activation, out_dtype):
+    return a.new_empty((*a.shape[:-1], b.shape[0]), dtype=out_dtype)
+
+
+def gemm_into(a, b, bias, residual, activation, out):
+    lead, (n, k) = tuple(a.shape[:-1]), b.shape
+    if tuple(out.shape) != (*lead, n):
+        raise ValueError(f"out must have the shape {(*lead, n)}, got {tuple(out.shape)}")
+    m = math.prod(lead)
+    if m == 0 or n == 0:
+        return
+    target = output_target(out, (a, b, bias), residual)
+    (a, a_stride), (b, b_stride) = readable_rows(a), readable_rows(b)
+    bias = bias_operand(bias)
+    residual, residual_stride = residual_operand(residual)
+    sizes = sizes_of(a_stride, b_stride, target, residual_stride, m, n, k, activation)
+    device = a.get_device()
+    _lib.check(_lib.library().zck_gemm_bf16(a.data_ptr(), b.data_ptr(), target.data_ptr(), address(bias),
+                                            address(residual), ctypes.byref(sizes), device, raw_stream(device)))
+    if target is not out:
+        out.copy_(target)
+
+
+GEMM = define(
+    "gemm",
+    params=[Param("Tensor", "a"), Param("Tensor", "b"), Param("Tensor?", "bias"), Param("Tensor?", "residual"),
+            Param("str", "activation"), Param("ScalarType", "out_dtype")],
+    outs=[Out("out", "out", gemm_output, "out_dtype")], check=check_gemm, check_sizes=check_gemm_sizes, run=gemm_into)
+gemm_op, gemm_out_op = GEMM.functional, GEMM.out
+
+
+def gemm(a, b, *, bias=None, activation="none", residual=None, out=None, out_dtype=torch.bfloat16):
+    """`F.linear(a, b, bias)` followed by `activation` and the addition of `residual`, BF16 in and out."""
+    return GEMM(a, b, bias, residual, activation, out_dtype, outputs={"out": out})
