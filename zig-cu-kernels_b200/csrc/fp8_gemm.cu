@@ -301,20 +301,44 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ptx::named_barrier(1, kEpilogueThreads);
             const bool last = sh->last != 0;
             ptx::named_barrier(1, kEpilogueThreads);  // `last` is read before the next unit may overwrite it
-            if (last && row_live) {
+            if (last) {
+                // All 256 epilogue threads add the partial tiles: float4 element e belongs to row e % live of column
+                // quad e / live, every element is summed in split order (so the bits do not depend on who was last),
+                // four loads in flight at a time, and lands in the slot of split 0. Then each row's owner reads its
+                // 128 sums back (they sit in L2) and runs the output phase.
                 __threadfence();
-                const float* first = p.parts + (uint64_t)(c.tile * p.splits) * kTileFloats + ((uint64_t)group * 32 * kBM + lane_row) * 4;
+                const uint32_t live = min((uint32_t)kBM, p.m - c.m0);
+                float* slot0 = p.parts + (uint64_t)(c.tile * p.splits) * kTileFloats;
+                for (uint32_t e = threadIdx.x; e < 64u * live; e += kEpilogueThreads) {
+                    float* at = slot0 + ((uint64_t)(e / live) * kBM + e % live) * 4;
+                    float4 sum = __ldcg(reinterpret_cast<const float4*>(at));
+                    for (uint32_t s0 = 1; s0 < p.splits; s0 += 4) {
+                        float4 v[4];
 #pragma unroll
-                for (int quad = 0; quad < 32; ++quad) {
-                    float4 sum = __ldcg(reinterpret_cast<const float4*>(first + (uint64_t)quad * kBM * 4));
-                    for (uint32_t s = 1; s < p.splits; ++s) {
-                        float4 v = __ldcg(reinterpret_cast<const float4*>(first + (uint64_t)s * kTileFloats + (uint64_t)quad * kBM * 4));
-                        sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
-                        sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+                        for (uint32_t j = 0; j < 4; ++j)
+                            if (s0 + j < p.splits) v[j] = __ldcg(reinterpret_cast<const float4*>(at + (uint64_t)(s0 + j) * kTileFloats));
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            if (s0 + j < p.splits) {
+                                sum.x = __fadd_rn(sum.x, v[j].x); sum.y = __fadd_rn(sum.y, v[j].y);
+                                sum.z = __fadd_rn(sum.z, v[j].z); sum.w = __fadd_rn(sum.w, v[j].w);
+                            }
+                        }
                     }
-                    acc[2 * quad] = make_float2(sum.x, sum.y); acc[2 * quad + 1] = make_float2(sum.z, sum.w);
+                    __stcg(reinterpret_cast<float4*>(at), sum);
                 }
-                write_row_any<GATED, ACT>(p, acc, row, col0);
+                __threadfence();
+                ptx::named_barrier(1, kEpilogueThreads);
+                if (row_live) {
+                    const float* mine = slot0 + ((uint64_t)group * 32 * kBM + lane_row) * 4;
+#pragma unroll
+                    for (int quad = 0; quad < 32; ++quad) {
+                        const float4 sum = __ldcg(reinterpret_cast<const float4*>(mine + (uint64_t)quad * kBM * 4));
+                        acc[2 * quad] = make_float2(sum.x, sum.y);
+                        acc[2 * quad + 1] = make_float2(sum.z, sum.w);
+                    }
+                    write_row_any<GATED, ACT>(p, acc, row, col0);
+                }
             }
             }  // SPLIT
         }
