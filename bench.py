@@ -97,7 +97,7 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
-def cpu_reference_tokens_per_s(sample_tokens, repeats):
+def cpu_reference_tokens_per_s(sample_tokens, repeats, warmup=0):
     """The CPU restatement of the reference's torch path (oracle/rules.py) on the first `sample_tokens` tokens of the
     workload, all host threads: rows-quantize, dequantise, FP32 matmuls, SwiGLU epilogue, rows-quantize, down."""
     from oracle import rules
@@ -116,6 +116,8 @@ def cpu_reference_tokens_per_s(sample_tokens, repeats):
         q, s_q = rules.quantize_rows(act)
         return rules.fp8_gemm(q, down, s_q, s_down, dtype=torch.float32)
 
+    for _ in range(warmup):
+        step()
     times = []
     for _ in range(repeats):
         start = time.perf_counter()
@@ -128,7 +130,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    rate, threads, seconds = cpu_reference_tokens_per_s(CPU_SAMPLE_TOKENS, max(1, args.steps))
+    rate, threads, seconds = cpu_reference_tokens_per_s(CPU_SAMPLE_TOKENS, max(1, args.steps), min(args.warmup, 3))
     sample = f"first {CPU_SAMPLE_TOKENS} of {M} tokens per step, weights quantized once outside the timed region"
     print(json.dumps({
         "impl": "reference", "metric": "tp_mlp_tokens_per_s", "value": rate, "unit": "tokens/s", "n_gpus": args.gpus,
