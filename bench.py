@@ -156,6 +156,7 @@ def main():
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--chunks", type=int, default=1, help="token chunks whose exchange overlaps the next GEMMs")
     parser.add_argument("--exchange", default="reduce_scatter", choices=("reduce_scatter", "all_reduce"))
+    parser.add_argument("--e2e-chunks", type=int, default=4, help="token chunks of the pipelined end-to-end step")
     parser.add_argument("--no-graphs", action="store_true", help="launch every op from Python instead of replaying CUDA graphs")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--tokens", type=int, default=M, help="token rows per step (smaller only for profiling)")
@@ -190,42 +191,28 @@ def main():
                             exchange=args.exchange)
     del w_gate, w_up, w_down
     torch.cuda.empty_cache()
-    # End-to-end step: every rank owns tokens_per_step / world rows in pinned host memory, copies them to the device,
-    # the ranks all-gather the token matrix over NVLink, run the MLP and each reads back what the exchange left it
-    # (its rows after reduce_scatter, all rows after all_reduce).
+    # End-to-end step: every rank owns tokens_per_step / world rows in pinned host memory (ordered chunk after chunk),
+    # copies them to the device, the ranks all-gather the token matrix over NVLink, run the MLP and each reads back what
+    # the exchange left it (its rows after reduce_scatter, all rows after all_reduce). The step is pipelined over
+    # --e2e-chunks token chunks: upload of chunk c+1 and download of chunk c-1 run under the kernels of chunk c.
     own = tokens_per_step // world
-    own_lo = rank * own
-    pinned_in = torch.empty(own, HIDDEN, dtype=tokens.dtype).pin_memory()
-    pinned_in.copy_(tokens[own_lo:own_lo + own])
     out_rows = own if (world > 1 and args.exchange == "reduce_scatter") else tokens_per_step
-    pinned_out = torch.empty(out_rows, HIDDEN, dtype=tokens.dtype).pin_memory()
     staged = torch.empty_like(tokens)
-    staged_own = staged[own_lo:own_lo + own] if world == 1 else torch.empty(own, HIDDEN, dtype=tokens.dtype, device=device)
+    device_step = mlp.graphed(tokens) if not args.no_graphs else (lambda: mlp.forward(tokens))
+    pipelined = mlp.graphed(staged, chunks=args.e2e_chunks)
+    pinned_in = torch.empty(own, HIDDEN, dtype=tokens.dtype).pin_memory()
+    from zig_cu_kernels.tp_mlp import exchange_plan
+    offset = 0
+    for lo, hi, _, _ in exchange_plan(tokens_per_step, world, args.e2e_chunks, args.exchange):
+        rows = (hi - lo) // world
+        pinned_in[offset:offset + rows].copy_(tokens[lo + rank * rows:lo + (rank + 1) * rows])
+        offset += rows
+    pinned_out = torch.empty(out_rows, HIDDEN, dtype=tokens.dtype).pin_memory()
 
-    def upload():
-        staged_own.copy_(pinned_in, non_blocking=True)
+    def e2e_step():
+        return pipelined(pinned_in, pinned_out)
 
-    def download(result):
-        pinned_out.copy_(result, non_blocking=True)
-
-    if args.no_graphs:
-        def device_step():
-            return mlp.forward(tokens)
-
-        def e2e_step():
-            upload()
-            result = mlp.forward(staged, staged_own)
-            download(result)
-            return result
-    else:
-        device_step = mlp.graphed(tokens)
-        replay_staged = mlp.graphed(staged)
-
-        def e2e_step():
-            upload()
-            result = replay_staged(staged_own)
-            download(result)
-            return result
+    e2e_step.finish = pipelined.finish
 
     def eager_step():
         return mlp.forward(tokens)
@@ -236,6 +223,8 @@ def main():
         start.record()
         for _ in range(steps):
             step()
+        if hasattr(step, "finish"):
+            step.finish()  # copies on the side streams belong to the timed region
         end.record()
         barrier()
         seconds = torch.tensor([start.elapsed_time(end) * 1e-3], device=device, dtype=torch.float64)

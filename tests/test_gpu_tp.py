@@ -26,3 +26,31 @@ def test_tensor_parallel_mlp_matches_one_gpu():
     done = subprocess.run(command, capture_output=True, text=True, timeout=600,
                           env={**__import__("os").environ, "NCCL_NVLS_ENABLE": "0"})
     assert done.returncode == 0 and "TP_CHECK_OK" in done.stdout, done.stdout[-2000:] + done.stderr[-4000:]
+
+
+def test_pipelined_end_to_end_step_on_one_gpu():
+    """The graph-replayed, chunk-pipelined step with pinned host buffers gives the bits of the plain forward pass,
+    step after step (each step reuses the device buffers of the one before)."""
+    import sys
+    sys.path[:0] = [str(ROOT / "zig-cu-kernels_b200")]
+    from zig_cu_kernels.tp_mlp import TensorParallelMLP
+
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    m, hidden, inter = 1024, 512, 1024
+    w_gate = (torch.randn(inter, hidden, device="cuda", generator=generator) / 22).bfloat16()
+    w_up = (torch.randn(inter, hidden, device="cuda", generator=generator) / 22).bfloat16()
+    w_down = (torch.randn(hidden, inter, device="cuda", generator=generator) / 32).bfloat16()
+    mlp = TensorParallelMLP(w_gate, w_up, w_down)
+    staged = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
+    replay = mlp.graphed(staged, chunks=4)
+    host_in = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
+    for step in range(3):
+        tokens = torch.randn(m, hidden, device="cuda", generator=generator).bfloat16()
+        expected = mlp.forward(tokens)
+        host_in.copy_(tokens)
+        torch.cuda.synchronize()
+        replay(host_in, host_out)
+        replay.finish()
+        torch.cuda.synchronize()
+        assert torch.equal(host_out.view(torch.int16), expected.cpu().view(torch.int16)), f"step {step}"

@@ -41,6 +41,23 @@ def main():
         error = float((result - expected).abs().max() / whole.abs().max())
         worst = max(worst, error)
         assert error <= 1e-2, f"rank {rank} {exchange} chunks={chunks}: max relative error {error}"
+    # the pipelined end-to-end step: own rows from pinned host memory, all-gather, MLP, reduce-scatter, rows back
+    mlp = TensorParallelMLP(w_gate, w_up, w_down, rank, world, exchange="reduce_scatter")
+    staged = torch.empty_like(tokens)
+    replay = mlp.graphed(staged, chunks=2)
+    plan = exchange_plan(m, world, 2, "reduce_scatter")
+    own = torch.cat([tokens[lo:hi].chunk(world)[rank] for lo, hi, _, _ in plan])
+    host_in = torch.empty(own.shape, dtype=own.dtype).pin_memory()
+    host_in.copy_(own)
+    host_out = torch.empty(m // world, hidden, dtype=torch.bfloat16).pin_memory()
+    expected = torch.cat([whole[lo:hi].chunk(world)[rank] for lo, hi, _, _ in plan])
+    for _ in range(2):
+        replay(host_in, host_out)
+        replay.finish()
+        torch.cuda.synchronize()
+        error = float((host_out.float().to(device) - expected).abs().max() / whole.abs().max())
+        worst = max(worst, error)
+        assert error <= 1e-2, f"rank {rank} pipelined step: max relative error {error}"
     errors = torch.tensor([worst], device=device)
     dist.all_reduce(errors, op=dist.ReduceOp.MAX)
     if rank == 0:

@@ -116,17 +116,25 @@ class TensorParallelMLP:
         compute.wait_stream(self.comm_stream)
         return result
 
-    def graphed(self, tokens):
+    def graphed(self, tokens, chunks=None):
         """Binds a replayable forward pass to the fixed buffer `tokens`: the four kernels of every token chunk are
         captured into one CUDA graph per chunk (one host launch instead of four op calls), while the collectives
-        stay ordinary NCCL calls between the replays. Returns `replay(own_rows=None) -> result`, same meaning as
-        `forward`. Kernel events cannot be collected from replays."""
+        stay ordinary NCCL calls between the replays. Returns `replay(host_in=None, host_out=None) -> result`.
+
+        Without arguments `replay` is `forward(tokens)`. With pinned host tensors it is an end-to-end step that is
+        pipelined chunk by chunk: this rank's rows of chunk c (`host_in`, `m / world` rows ordered chunk after chunk)
+        go to the device on a copy stream while chunk c-1 computes, the ranks all-gather the chunk over NVLink, and
+        what the exchange leaves this rank of chunk c (`host_out`: its `m / world` rows after reduce_scatter, all `m`
+        rows otherwise) goes back on a third stream while chunk c+1 computes. `replay.finish()` makes the current
+        stream wait for the copies still in flight. Kernel events cannot be collected from replays."""
+        import torch.distributed as dist
+
         m = tokens.shape[0]
+        device = tokens.device
         scatter = self.world > 1 and self.exchange == "reduce_scatter"
-        plan = exchange_plan(m, self.world, self.chunks if self.world > 1 else 1, self.exchange)
-        partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=tokens.device)
-        result = torch.empty(m // self.world, self.hidden, dtype=torch.bfloat16, device=tokens.device) if scatter \
-            else partial
+        plan = exchange_plan(m, self.world, self.chunks if chunks is None else chunks, self.exchange)
+        partial = torch.empty(m, self.hidden, dtype=torch.bfloat16, device=device)
+        result = torch.empty(m // self.world, self.hidden, dtype=torch.bfloat16, device=device) if scatter else partial
         events, self.kernel_events = self.kernel_events, None
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
@@ -144,28 +152,66 @@ class TensorParallelMLP:
             graphs.append(graph)
         self.kernel_events = events
 
-        def replay(own_rows=None):
-            import torch.distributed as dist
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        own = [torch.empty((hi - lo) // self.world, self.hidden, dtype=tokens.dtype, device=device)
+               for lo, hi, _, _ in plan] if self.world > 1 else None
+        uploaded = [torch.cuda.Event() for _ in plan]   # chunk c of this step is on the device
+        consumed = [torch.cuda.Event() for _ in plan]   # chunk c of the tokens has been read by its kernels
+        produced = [torch.cuda.Event() for _ in plan]   # chunk c of the result is final
+        downloaded = [torch.cuda.Event() for _ in plan]  # chunk c of the result is on the host
+        state = {"steps": 0}
 
-            if own_rows is not None:
-                if self.world > 1:
-                    dist.all_gather_into_tensor(tokens, own_rows, group=self.group)
-                elif own_rows.data_ptr() != tokens.data_ptr():
-                    tokens.copy_(own_rows)
+        def replay(host_in=None, host_out=None):
             compute = torch.cuda.current_stream()
-            for graph, (lo, hi, result_lo, result_hi) in zip(graphs, plan):
+            first = state["steps"] == 0
+            state["steps"] += 1
+            if host_in is not None:
+                offset = 0
+                with torch.cuda.stream(copy_in):
+                    for c, (lo, hi, _, _) in enumerate(plan):
+                        rows = (hi - lo) // self.world
+                        if not first:
+                            copy_in.wait_event(consumed[c])  # the previous step is done with this chunk's buffer
+                        target = own[c] if self.world > 1 else tokens[lo:hi]
+                        target.copy_(host_in[offset:offset + rows], non_blocking=True)
+                        uploaded[c].record(copy_in)
+                        offset += rows
+            offset = 0
+            for c, (graph, (lo, hi, result_lo, result_hi)) in enumerate(zip(graphs, plan)):
+                if host_in is not None:
+                    compute.wait_event(uploaded[c])
+                    if self.world > 1:
+                        dist.all_gather_into_tensor(tokens[lo:hi], own[c], group=self.group)
+                if host_out is not None and not first:
+                    compute.wait_event(downloaded[c])  # the previous step's result chunk has left the device
                 graph.replay()
                 self.launches += 4
-                if self.world == 1:
-                    continue
-                self.comm_stream.wait_stream(compute)
-                with torch.cuda.stream(self.comm_stream):
-                    if scatter:
-                        dist.reduce_scatter_tensor(result[result_lo:result_hi], partial[lo:hi], group=self.group)
-                    else:
-                        dist.all_reduce(partial[lo:hi], group=self.group)
+                consumed[c].record(compute)
+                if self.world > 1:
+                    self.comm_stream.wait_stream(compute)
+                    with torch.cuda.stream(self.comm_stream):
+                        if scatter:
+                            dist.reduce_scatter_tensor(result[result_lo:result_hi], partial[lo:hi], group=self.group)
+                        else:
+                            dist.all_reduce(partial[lo:hi], group=self.group)
+                        produced[c].record(self.comm_stream)
+                else:
+                    produced[c].record(compute)
+                if host_out is not None:
+                    piece = result[result_lo:result_hi]
+                    with torch.cuda.stream(copy_out):
+                        copy_out.wait_event(produced[c])
+                        host_out[offset:offset + piece.shape[0]].copy_(piece, non_blocking=True)
+                        downloaded[c].record(copy_out)
+                    offset += piece.shape[0]
             if self.world > 1:
                 compute.wait_stream(self.comm_stream)
             return result
 
+        def finish():
+            compute = torch.cuda.current_stream()
+            compute.wait_stream(copy_in)
+            compute.wait_stream(copy_out)
+
+        replay.finish = finish
         return replay
