@@ -31,6 +31,10 @@ SEED = 4
 FLOPS_PER_TOKEN = 6 * HIDDEN * INTER
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 CPU_SAMPLE_TOKENS = 128
+# DRAM bytes of one gated-GEMM launch on 4096 tokens (one band of the tile walk), dram__bytes_read.sum +
+# dram__bytes_write.sum from the ncu capture summarised in profiles/fp8_gemm_kernel_4096_tokens_dram_traffic.md.
+# A 16384-token launch walks four such bands, each streaming the weights once, so its traffic is four times this.
+GATED_TRAFFIC_PER_4096_TOKENS = 629462016 + 227042560
 
 
 def peaks():
@@ -157,6 +161,7 @@ def main():
     parser.add_argument("--chunks", type=int, default=1, help="token chunks whose exchange overlaps the next GEMMs")
     parser.add_argument("--exchange", default="reduce_scatter", choices=("reduce_scatter", "all_reduce"))
     parser.add_argument("--e2e-chunks", type=int, default=4, help="token chunks of the pipelined end-to-end step")
+    parser.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave the end-to-end step out")
     parser.add_argument("--no-graphs", action="store_true", help="launch every op from Python instead of replaying CUDA graphs")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--tokens", type=int, default=M, help="token rows per step (smaller only for profiling)")
@@ -199,7 +204,9 @@ def main():
     out_rows = own if (world > 1 and args.exchange == "reduce_scatter") else tokens_per_step
     staged = torch.empty_like(tokens)
     device_step = mlp.graphed(tokens) if not args.no_graphs else (lambda: mlp.forward(tokens))
-    pipelined = mlp.graphed(staged, chunks=args.e2e_chunks)
+    pipelined = (lambda *_: None) if args.skip_e2e else mlp.graphed(staged, chunks=args.e2e_chunks)
+    if args.skip_e2e:
+        pipelined.finish = lambda: None
     pinned_in = torch.empty(own, HIDDEN, dtype=tokens.dtype).pin_memory()
     from zig_cu_kernels.tp_mlp import exchange_plan
     offset = 0
@@ -274,13 +281,18 @@ def main():
         "config": dict(workload_config(world, args.exchange), tokens_per_step=tokens_per_step, chunks=args.chunks,
                        launch="python ops" if args.no_graphs else "cuda graph replay of the kernels, NCCL calls between replays"),
         "tflops": tokens_per_step * FLOPS_PER_TOKEN * args.steps / device_seconds / 1e12,
-        "e2e": {"value": tokens_per_step * args.steps / e2e_seconds, "unit": "tokens/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
+        "e2e": None if args.skip_e2e else {"value": tokens_per_step * args.steps / e2e_seconds, "unit": "tokens/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
                 "h2d_bytes_per_step": own * HIDDEN * 2 * world,
                 "d2h_bytes_per_step": out_rows * HIDDEN * 2 * world},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"kernel": "fp8_gemm_kernel<gated> (fp8_gated_gemm)", "bound": "tensor", "achieved": gated_tflops,
-                     "peak": fp8_peak, "unit": "TFLOP/s", "frac": gated_tflops / fp8_peak, "traffic": None,
+                     "peak": fp8_peak, "unit": "TFLOP/s", "frac": gated_tflops / fp8_peak,
+                     "traffic": (GATED_TRAFFIC_PER_4096_TOKENS * (tokens_per_step // 4096)
+                                 if world == 1 and tokens_per_step % 4096 == 0 and launches_per_step["gated_gemm"] == 1
+                                 else None),
+                     "algorithmic_bytes": tokens_per_step * HIDDEN + 2 * (INTER // world) * HIDDEN +
+                     2 * tokens_per_step * (INTER // world),
                      "peak_source": f"2 x bf16_tflops_sustained of {source} MEASURED_PEAKS.json"},
         "kernels": {"gated_gemm_tflops": gated_tflops, "down_gemm_tflops": down_tflops,
                     "quantize_rows_gbs": rows_gbs, "hbm_peak_gbs": measured["hbm_gbs"],

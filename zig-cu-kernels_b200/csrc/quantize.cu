@@ -6,6 +6,8 @@
 #include "zck_device.cuh"
 #include "zck_host.h"
 
+#include <type_traits>
+
 namespace zck {
 
 template <typename T>
@@ -44,19 +46,26 @@ __device__ __forceinline__ float octet_amax(const Octet<T>& o, float amax) {
     return amax;
 }
 
-// Codes of one octet. FP32 scale: x / scale; E8M0 scale: x * 2^(127-b), the same real number, correctly rounded.
-template <typename T, bool E8M0>
+// How the values of a group become quotients: by the exact power-of-two factor of an E8M0 scale, by the corrected
+// reciprocal of a GroupDivider that is `fast`, or by plain division. The choice is made once per group, outside the
+// loops over its values.
+enum Quotient { kByFactor, kByCorrection, kByDivision };
+
+template <typename T, Quotient HOW>
 __device__ __forceinline__ uint2 octet_codes(const Octet<T>& o, const GroupDivider& divide) {
     float q[8];
 #pragma unroll
     for (int i = 0; i < 8; i += 2) {
-        if (E8M0) {
+        if (HOW == kByFactor) {
             q[i] = __fmul_rn(o.get(i), divide.scale);
             q[i + 1] = __fmul_rn(o.get(i + 1), divide.scale);
-        } else {
-            const float2 two = divide.pair(o.get(i), o.get(i + 1));
+        } else if (HOW == kByCorrection) {
+            const float2 two = divide.corrected(o.get(i), o.get(i + 1));
             q[i] = two.x;
             q[i + 1] = two.y;
+        } else {
+            q[i] = __fdiv_rn(o.get(i), divide.scale);
+            q[i + 1] = __fdiv_rn(o.get(i + 1), divide.scale);
         }
     }
     return make_uint2(e4m3x4_of(q[0], q[1], q[2], q[3]), e4m3x4_of(q[4], q[5], q[6], q[7]));
@@ -71,22 +80,26 @@ __device__ __forceinline__ uint2 octet_codes(const Octet<T>& o, const GroupDivid
 constexpr int kRowsThreads = 256;
 constexpr int kRowsSlotsPerBlock = kRowsThreads / 8;
 
-template <typename T, bool E8M0, typename Index>
+template <typename T, bool E8M0>
 __global__ void __launch_bounds__(kRowsThreads)
 quantize_rows_kernel(const T* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ codes, void* __restrict__ scales,
                      uint64_t scale_stride, uint32_t m, uint32_t groups_per_row) {
     const uint32_t lane = threadIdx.x & 7;
-    const Index total = (Index)m * groups_per_row;
-    const Index stride = (Index)gridDim.x * kRowsSlotsPerBlock;
-    Index slot = (Index)blockIdx.x * kRowsSlotsPerBlock + threadIdx.x / 8;
+    const uint64_t total = (uint64_t)m * groups_per_row;
+    const uint64_t stride = (uint64_t)gridDim.x * kRowsSlotsPerBlock;
+    // The only divisions of the kernel: where this thread starts and how far (rows, groups) one grid stride moves it.
+    // After that (row, g) advance by additions; the host keeps m far enough below 2^32 for `row` of a dead slot.
+    const uint32_t step_rows = (uint32_t)(stride / groups_per_row), step_groups = (uint32_t)(stride % groups_per_row);
+    const uint64_t block_first = (uint64_t)blockIdx.x * kRowsSlotsPerBlock;
+    uint32_t row = (uint32_t)((block_first + threadIdx.x / 8) / groups_per_row);
+    uint32_t g = (uint32_t)((block_first + threadIdx.x / 8) % groups_per_row);
     // Every thread of a warp runs the same number of iterations (the shuffles need all 32 lanes): the trip count is
-    // taken from the first slot of the block, and slots past the end are dead.
-    const Index block_first = (Index)blockIdx.x * kRowsSlotsPerBlock;
+    // taken from the first slot of the block, and slots past the end (row >= m) are dead.
+    const uint64_t trips = block_first < total ? (total - block_first + stride - 1) / stride : 0;
     Octet<T> next0, next1;
-    auto fetch = [&](Index at, Octet<T>& a, Octet<T>& b) {
-        if (at < total) {
-            const uint32_t row = (uint32_t)(at / groups_per_row), g = (uint32_t)(at % groups_per_row);
-            const T* source = x + (uint64_t)row * x_stride + (uint64_t)g * kGroup;
+    auto fetch = [&](uint32_t at_row, uint32_t at_g, Octet<T>& a, Octet<T>& b) {
+        if (at_row < m) {
+            const T* source = x + (uint64_t)at_row * x_stride + (uint64_t)at_g * kGroup;
             a.load(source + 8 * lane);
             b.load(source + 8 * (8 + lane));
         } else {
@@ -94,29 +107,49 @@ quantize_rows_kernel(const T* __restrict__ x, uint64_t x_stride, uint8_t* __rest
             b.zero();
         }
     };
-    fetch(slot, next0, next1);
-    for (Index first = block_first; first < total; first += stride, slot += stride) {
+    fetch(row, g, next0, next1);
+    for (uint64_t trip = 0; trip < trips; ++trip) {
         const Octet<T> o0 = next0, o1 = next1;
-        fetch(slot + stride, next0, next1);
-        const bool live = slot < total;
-        const uint32_t row = live ? (uint32_t)(slot / groups_per_row) : 0, g = live ? (uint32_t)(slot % groups_per_row) : 0;
+        const uint32_t row_now = row, g_now = g;
+        row += step_rows;
+        g += step_groups;
+        if (g >= groups_per_row) {
+            g -= groups_per_row;
+            ++row;
+        }
+        fetch(row, g, next0, next1);
+        const bool live = row_now < m;
         float amax = octet_amax(o1, octet_amax(o0, 0.0f));
         amax = max_nan_over_lanes<8>(amax);  // the xor masks 4, 2, 1 stay inside each group of 8 lanes
         float operand;
         if (E8M0) {
             uint32_t byte = scale_e8m0_of(amax);
             operand = e8m0_reciprocal(byte);
-            if (live && lane == 0) static_cast<uint8_t*>(scales)[(uint64_t)g * scale_stride + row] = (uint8_t)byte;
+            if (live && lane == 0) static_cast<uint8_t*>(scales)[(uint64_t)g_now * scale_stride + row_now] = (uint8_t)byte;
         } else {
             operand = scale_f32_of(amax);
-            if (live && lane == 0) static_cast<float*>(scales)[(uint64_t)g * scale_stride + row] = operand;
+            if (live && lane == 0) static_cast<float*>(scales)[(uint64_t)g_now * scale_stride + row_now] = operand;
         }
         if (live) {
-            // For E8M0 the "divider" only carries the power-of-two factor 2^(127-b) that multiplies every value.
-            const GroupDivider divide = GroupDivider::of(operand);
-            uint8_t* target = codes + ((uint64_t)row * groups_per_row + g) * kGroup;
-            st_global_v2(target + 8 * lane, octet_codes<T, E8M0>(o0, divide));
-            st_global_v2(target + 8 * (8 + lane), octet_codes<T, E8M0>(o1, divide));
+            uint8_t* target = codes + ((uint64_t)row_now * groups_per_row + g_now) * kGroup;
+            uint2 c0, c1;
+            if (E8M0) {
+                GroupDivider factor;  // only carries the power of two 2^(127-b) that multiplies every value
+                factor.scale = operand;
+                c0 = octet_codes<T, kByFactor>(o0, factor);
+                c1 = octet_codes<T, kByFactor>(o1, factor);
+            } else {
+                const GroupDivider divide = GroupDivider::of(operand);
+                if (divide.fast) {
+                    c0 = octet_codes<T, kByCorrection>(o0, divide);
+                    c1 = octet_codes<T, kByCorrection>(o1, divide);
+                } else {
+                    c0 = octet_codes<T, kByDivision>(o0, divide);
+                    c1 = octet_codes<T, kByDivision>(o1, divide);
+                }
+            }
+            st_global_v2(target + 8 * lane, c0);
+            st_global_v2(target + 8 * (8 + lane), c1);
         }
     }
 }
@@ -161,13 +194,21 @@ quantize_tiles_kernel(const T* __restrict__ w, uint64_t w_stride, uint8_t* __res
         operand = scale_f32_of(amax);
         if (threadIdx.x == 0) static_cast<float*>(scales)[(uint64_t)tile_row * scale_stride + tile_col] = operand;
     }
-    const GroupDivider divide = GroupDivider::of(operand);
+    GroupDivider divide;
+    if (E8M0) divide.scale = operand;  // the power of two 2^(127-b) that multiplies every value
+    else divide = GroupDivider::of(operand);
     uint8_t* target = codes + (uint64_t)first_row * k + (uint64_t)tile_col * kGroup + 8 * o;
+    auto store_as = [&](auto how) {
 #pragma unroll
-    for (int pass = 0; pass < 8; ++pass) {
-        uint32_t row = pass * 16 + r;
-        if (first_row + row < n) st_global_v2(target + (uint64_t)row * k, octet_codes<T, E8M0>(held[pass], divide));
-    }
+        for (int pass = 0; pass < 8; ++pass) {
+            uint32_t row = pass * 16 + r;
+            if (first_row + row < n)
+                st_global_v2(target + (uint64_t)row * k, octet_codes<T, decltype(how)::value>(held[pass], divide));
+        }
+    };
+    if (E8M0) store_as(std::integral_constant<Quotient, kByFactor>());
+    else if (divide.fast) store_as(std::integral_constant<Quotient, kByCorrection>());
+    else store_as(std::integral_constant<Quotient, kByDivision>());
 }
 
 static int check_quantizer(const void* x, int kind, uint64_t stride, const void* codes, const void* scales,
@@ -204,26 +245,20 @@ extern "C" int zck_quantize_fp8_rows(const void* x, int x_kind, uint64_t x_strid
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     dim3 threads(kRowsThreads);
     uint8_t* q = static_cast<uint8_t*>(codes);
-    // 32-bit slot arithmetic (one division per slot) whenever the slot count and the grid stride allow it.
-    const bool narrow = slots + (uint64_t)state->sm_count * 8 * kRowsSlotsPerBlock < 0xFFFFFFFFull;
+    ZCK_REQUIRE(m <= 0xFFF00000u, "x has too many rows for one launch: %u", m);
     // The grid is persistent, so it holds exactly the blocks that are resident at once (asked of the runtime once per
     // kernel instance).
-#define ZCK_ROWS_AS(T, E, I)                                                                                              \
-    do {                                                                                                                  \
-        static int per_sm = 0;                                                                                            \
-        if (per_sm == 0) {                                                                                                \
-            int blocks = 0;                                                                                               \
-            ZCK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, quantize_rows_kernel<T, E, I>, kRowsThreads, 0)); \
-            per_sm = blocks > 0 ? blocks : 1;                                                                             \
-        }                                                                                                                 \
-        uint64_t resident = (uint64_t)state->sm_count * per_sm;                                                           \
-        dim3 grid((unsigned)(needed < resident ? needed : resident));                                                     \
-        quantize_rows_kernel<T, E, I><<<grid, threads, 0, s>>>(static_cast<const T*>(x), x_stride, q, scales, scale_stride, m, groups_per_row); \
-    } while (0)
-#define ZCK_ROWS(T, E)                                   \
-    do {                                                 \
-        if (narrow) ZCK_ROWS_AS(T, E, uint32_t);         \
-        else ZCK_ROWS_AS(T, E, uint64_t);                \
+#define ZCK_ROWS(T, E)                                                                                                 \
+    do {                                                                                                               \
+        static int per_sm = 0;                                                                                         \
+        if (per_sm == 0) {                                                                                             \
+            int blocks = 0;                                                                                            \
+            ZCK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, quantize_rows_kernel<T, E>, kRowsThreads, 0)); \
+            per_sm = blocks > 0 ? blocks : 1;                                                                          \
+        }                                                                                                              \
+        uint64_t resident = (uint64_t)state->sm_count * per_sm;                                                        \
+        dim3 grid((unsigned)(needed < resident ? needed : resident));                                                  \
+        quantize_rows_kernel<T, E><<<grid, threads, 0, s>>>(static_cast<const T*>(x), x_stride, q, scales, scale_stride, m, groups_per_row); \
     } while (0)
     if (x_kind == ZCK_BF16) {
         if (scale_is_e8m0) ZCK_ROWS(__nv_bfloat16, true); else ZCK_ROWS(__nv_bfloat16, false);
@@ -231,7 +266,6 @@ extern "C" int zck_quantize_fp8_rows(const void* x, int x_kind, uint64_t x_strid
         if (scale_is_e8m0) ZCK_ROWS(float, true); else ZCK_ROWS(float, false);
     }
 #undef ZCK_ROWS
-#undef ZCK_ROWS_AS
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }

@@ -75,30 +75,27 @@ struct GroupDivider {
         d.fast = exponent >= 127u - 60u && exponent <= 127u + 60u;
         return d;
     }
-    __device__ __forceinline__ float operator()(float x) const {
-        if (fast) {
-            const float q = __fmul_rn(x, reciprocal);
-            const float remainder = __fmaf_rn(-q, scale, x);
-            const float rounded = __fmaf_rn(remainder, reciprocal, q);
-            // The scale is positive, so the quotient has the sign of x; the correction step alone would turn an
-            // exact -0 into +0 (a zero remainder is +0).
-            return __uint_as_float((__float_as_uint(rounded) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
-        }
-        return __fdiv_rn(x, scale);
+    // One quotient of a group whose divider is `fast`.
+    __device__ __forceinline__ float corrected(float x) const {
+        const float q = __fmul_rn(x, reciprocal);
+        const float remainder = __fmaf_rn(-q, scale, x);
+        const float rounded = __fmaf_rn(remainder, reciprocal, q);
+        // The scale is positive, so the quotient has the sign of x; the correction step alone would turn an exact
+        // -0 into +0 (a zero remainder is +0).
+        return __uint_as_float((__float_as_uint(rounded) & 0x7FFFFFFFu) | (__float_as_uint(x) & 0x80000000u));
     }
-    // Two quotients at once with the two-wide FP32 FMA (x * r as fma(x, r, -0), which keeps every sign).
-    __device__ __forceinline__ float2 pair(float x0, float x1) const {
-        if (fast) {
-            const float2 x = make_float2(x0, x1), r = make_float2(reciprocal, reciprocal);
-            const float2 q = __ffma2_rn(x, r, make_float2(-0.0f, -0.0f));
-            const float2 remainder = __ffma2_rn(q, make_float2(-scale, -scale), x);
-            const float2 rounded = __ffma2_rn(remainder, r, q);
-            return make_float2(
-                __uint_as_float((__float_as_uint(rounded.x) & 0x7FFFFFFFu) | (__float_as_uint(x0) & 0x80000000u)),
-                __uint_as_float((__float_as_uint(rounded.y) & 0x7FFFFFFFu) | (__float_as_uint(x1) & 0x80000000u)));
-        }
-        return make_float2(__fdiv_rn(x0, scale), __fdiv_rn(x1, scale));
+    // Two such quotients with the two-wide FP32 FMA (x * r as fma(x, r, -0), which keeps every sign).
+    __device__ __forceinline__ float2 corrected(float x0, float x1) const {
+        const float2 x = make_float2(x0, x1), r = make_float2(reciprocal, reciprocal);
+        const float2 q = __ffma2_rn(x, r, make_float2(-0.0f, -0.0f));
+        const float2 remainder = __ffma2_rn(q, make_float2(-scale, -scale), x);
+        const float2 rounded = __ffma2_rn(remainder, r, q);
+        return make_float2(
+            __uint_as_float((__float_as_uint(rounded.x) & 0x7FFFFFFFu) | (__float_as_uint(x0) & 0x80000000u)),
+            __uint_as_float((__float_as_uint(rounded.y) & 0x7FFFFFFFu) | (__float_as_uint(x1) & 0x80000000u)));
     }
+    // Any group: callers with many values test `fast` once themselves and use `corrected` or __fdiv_rn directly.
+    __device__ __forceinline__ float operator()(float x) const { return fast ? corrected(x) : __fdiv_rn(x, scale); }
 };
 
 // Two FP32 values to two E4M3 bytes: round to nearest even, magnitudes above 448 clamp to 448, NaN gives 0x7F.
