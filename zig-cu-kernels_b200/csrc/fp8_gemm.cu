@@ -7,8 +7,9 @@
 // hardware block-scaling path (that path takes E8M0 only), hence the promotion in CUDA cores.
 //
 // Warp roles (384 threads): 0-7 epilogue (warpgroup g owns TMEM columns g*128..g*128+127; warp w reads lanes
-// 32*(w%4)..), 8 TMA producer, 9 MMA issuer and TMEM owner, 10-11 idle. The third warpgroup hands most of its
-// registers to the epilogue warpgroups, which hold 128 accumulators per thread.
+// 32*(w%4)..), 8 TMA producer, 9 MMA issuer and TMEM owner, 10 block-scale producer (fills a 16-deep ring of
+// per-K-block scales in shared memory), 11 idle. The third warpgroup hands most of its registers to the epilogue
+// warpgroups, which hold 128 accumulators per thread.
 // Shared memory: 4 stages x (A 128x128 + B 256x128 bytes) = 192 KiB in the 128-byte swizzle layout.
 // Gated (SwiGLU) tiles put [gate 0-63 | up 0-63 | gate 64-127 | up 64-127] rows of the weights into the B tile, so
 // a thread owns the gate and up sums of the same 64 output columns.
@@ -51,6 +52,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_addr(&sh->tmem_full[b]), 1);
             ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), (PAIR ? 2 : 1) * kEpilogueThreads / 32);
+        }
+        for (int s = 0; s < kScaleSlots; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&sh->scale_full[s]), 32);                     // the lanes of the scale warp
+            ptx::mbar_init(ptx::smem_addr(&sh->scale_empty[s]), kEpilogueThreads / 32);  // the epilogue warps
         }
         ptx::mbar_init(ptx::smem_addr(&sh->drain), 1);
         sh->abort = 0;
@@ -168,12 +173,60 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         }
         __syncwarp();
+      } else if (warp == kScaleWarp) {
+        // Lane l brings the scales of rows 4l .. 4l+3 of this CTA's tile; lanes 0-3 also bring the weight scale
+        // (l & 1: up) of epilogue warpgroup l >> 1. All-FP32 launches copy asynchronously (cp.async straight into the
+        // ring, the slot's barrier counts the copies' completion; one 16-byte copy per lane when the four row scales
+        // are contiguous and aligned, as in the layout the quantizer writes); launches with any E8M0 scale load,
+        // decode and store, which exposes the load latency once per K block but keeps one protocol per launch.
+        // The lanes do not vote on a wait that gave up: whoever gives up leaves, the others follow when their own
+        // wait ends (the abort flag is set), and nobody needs the others to make progress.
+        const bool all_f32 = (p.e8m0_bits & (GATED ? 7u : 3u)) == 0u;
+        const bool packed_rows = p.sa_row == 1 && p.sa_blk % 4 == 0 && (reinterpret_cast<uintptr_t>(p.scale_a) & 15u) == 0;
+        const uint32_t wg = (lane >> 1) & 1u, up = lane & 1u;
+        const bool brings_weight = lane < 4 && (GATED || up == 0);
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
+            const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
+            const uint32_t row0 = c.m0 + 4 * lane;
+            const uint32_t live_rows = row0 < p.m ? min(4u, p.m - row0) : 0u;  // rows past the end of A are never read back
+            const uint32_t weight_tile = min((c.n0 + wg * (GATED ? 64 : 128)) / kGroup, (p.n - 1) / kGroup);
+            // Element indices of this lane's first row scale and of its weight scale for the unit's first K block.
+            uint64_t row_at = (uint64_t)row0 * p.sa_row + (uint64_t)c.kb0 * p.sa_blk;
+            uint64_t weight_at = (uint64_t)weight_tile * (up ? p.su_row : p.sb_row) + (uint64_t)c.kb0 * (up ? p.su_blk : p.sb_blk);
+            for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                const uint32_t slot = it % kScaleSlots, phase = (it / kScaleSlots) & 1u;
+                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->scale_empty[slot]), phase ^ 1u, p, kRoleScales, slot))) break;
+                ScaleSlot* target = &sh->scales[slot];
+                const uint32_t full = ptx::smem_addr(&sh->scale_full[slot]);
+                if (all_f32) {
+                    if (packed_rows) {
+                        if (live_rows) copy_scales_async16(&target->row[4 * lane], p.scale_a, row_at, 4 * live_rows);
+                    } else {
+                        for (uint32_t r = 0; r < live_rows; ++r)
+                            copy_scale_async(&target->row[4 * lane + r], p.scale_a, row_at + r * p.sa_row);
+                    }
+                    if (brings_weight) copy_scale_async(&target->weight[wg][up], up ? p.scale_u : p.scale_b, weight_at);
+                    ptx::cp_async_mbar_arrive(full);
+                } else {
+                    for (uint32_t r = 0; r < live_rows; ++r)
+                        target->row[4 * lane + r] = load_scale(p.scale_a, row_at + r * p.sa_row, p.e8m0_bits & 1u);
+                    if (brings_weight)
+                        target->weight[wg][up] = load_scale(up ? p.scale_u : p.scale_b, weight_at, p.e8m0_bits & (up ? 4u : 2u));
+                    ptx::mbar_arrive(full);  // release: the stores above are visible to whoever sees the phase end
+                }
+                row_at += p.sa_blk;
+                weight_at += up ? p.su_blk : p.sb_blk;
+            }
+        }
+        ptx::cp_async_wait_all();  // nothing may land in shared memory after the block has left
+        __syncwarp();
       }
     } else {
         ptx::reg_take<kEpilogueRegs>();
         const uint32_t group = warp / 4, quarter = warp % 4;
         const uint32_t lane_row = quarter * 32 + lane;
-        const bool sa_e8m0 = p.e8m0_bits & 1u, sb_e8m0 = p.e8m0_bits & 2u, su_e8m0 = p.e8m0_bits & 4u;
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
@@ -181,64 +234,29 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             const uint32_t row = c.m0 + lane_row;
             const bool row_live = row < p.m;
             const bool warp_live = c.m0 + quarter * 32 < p.m;
-            // Output columns of this thread and the weight scale tile they fall in.
-            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);
-            const uint32_t scale_tile = min(col0 / kGroup, (p.n - 1) / kGroup);
+            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);  // first output column of this thread
             float2 acc[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
-            // Scales come through shared memory, two chunks of kScaleChunk K blocks ahead of their use. Every thread
-            // stages the scale of its own row; lanes 0-7 (8-15) of each warp stage the weight (up) scales of the
-            // warp, which the other lanes read after a warp barrier.
-            const uint64_t sa_base = (uint64_t)row * p.sa_row, sb_base = (uint64_t)scale_tile * p.sb_row,
-                           su_base = (uint64_t)scale_tile * p.su_row;
-            const uint32_t chunks = (c.kb_count + kScaleChunk - 1) / kScaleChunk;
-            auto stage_chunk = [&](uint32_t chunk) {
-                if (chunk < chunks) {
-                    const uint32_t first = chunk * kScaleChunk, buffer = chunk & 1u;
-                    if (row_live) {
-#pragma unroll
-                        for (uint32_t j = 0; j < (uint32_t)kScaleChunk; ++j)
-                            if (first + j < c.kb_count)
-                                stage_scale(&sh->scale_a[buffer][j][threadIdx.x], p.scale_a,
-                                            sa_base + (uint64_t)(c.kb0 + first + j) * p.sa_blk, sa_e8m0);
-                    }
-                    const uint32_t j = lane % kScaleChunk;
-                    if (first + j < c.kb_count) {
-                        if (lane < (uint32_t)kScaleChunk)
-                            stage_scale(&sh->scale_w[warp][buffer][0][j], p.scale_b,
-                                        sb_base + (uint64_t)(c.kb0 + first + j) * p.sb_blk, sb_e8m0);
-                        else if (GATED && lane < 2u * kScaleChunk)
-                            stage_scale(&sh->scale_w[warp][buffer][1][j], p.scale_u,
-                                        su_base + (uint64_t)(c.kb0 + first + j) * p.su_blk, su_e8m0);
-                    }
-                }
-                stage_commit();  // an empty group keeps the group count in step with the chunk count
-            };
-            __syncwarp();  // the previous unit's reads of the weight scales are over
-            stage_chunk(0);
-            stage_chunk(1);
             for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
                 const uint32_t kb = c.kb0 + i;
                 const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
-                const uint32_t chunk = i / kScaleChunk, j = i % kScaleChunk;
-                if (j == 0) {
-                    stage_wait<1>();  // everything but the newest chunk has landed
-                    __syncwarp();
-                }
-                const float sa = sh->scale_a[chunk & 1u][j][threadIdx.x];
-                const float f0 = __fmul_rn(sa, sh->scale_w[warp][chunk & 1u][0][j]);
-                const float f1 = GATED ? __fmul_rn(sa, sh->scale_w[warp][chunk & 1u][1][j]) : f0;
-                if (j == kScaleChunk - 1 || i + 1 == c.kb_count) {
-                    __syncwarp();  // every lane has read this chunk's weight scales before its buffer is refilled
-                    if (j == kScaleChunk - 1) stage_chunk(chunk + 2);
-                }
+                // The K block's scales wait in the ring (the scale warp runs kScaleSlots blocks ahead).
+                const uint32_t slot = it % kScaleSlots;
+                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->scale_full[slot]), (it / kScaleSlots) & 1u, p, kRoleEpilogue, 0x10000u + kb))) break;
+                const ScaleSlot* scales = &sh->scales[slot];
+                const float sa = scales->row[lane_row];
+                const float f0 = __fmul_rn(sa, scales->weight[group][0]);
+                const float f1 = GATED ? __fmul_rn(sa, scales->weight[group][1]) : f0;
+                __syncwarp();  // every lane has its scales in registers: the slot can go back
+                if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->scale_empty[slot]));
                 if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, kb))) break;
                 ptx::tc_fence_after();
                 if (warp_live) {
                     // Drain in four chunks of 32 columns through two register buffers: the loads of chunks 2 and 3
                     // are in flight while chunks 0 and 1 are folded in, and the buffer goes back to the tensor core
-                    // as soon as the last load has landed, before the last FMAs.
+                    // as soon as the last load has landed, before the last FMAs. (Requesting the next K block's first
+                    // chunks under those last FMAs was measured and lost 10%.)
                     const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + group * 128u;
                     const float2 f0x2 = make_float2(f0, f0), f1x2 = make_float2(f1, f1);
                     uint32_t even[32], odd[32];
@@ -271,7 +289,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        // The MMA thread that reuses the buffer sits in the leader CTA of a pair.
                         if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_addr(&sh->tmem_empty[buf]), 0));
                         else ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
                     }

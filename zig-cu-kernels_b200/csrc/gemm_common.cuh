@@ -15,7 +15,7 @@ constexpr int kStages = 4;
 constexpr int kATile = kBM * kBK, kBTile = kBN * kBK, kStageBytes = kATile + kBTile;
 constexpr int kBoxRows = 64;  // rows of one B box
 constexpr int kThreads = 384, kEpilogueThreads = 256;  // three warpgroups: two epilogue, one for the copy and MMA warps
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kProducerWarp = 8, kMmaWarp = 9, kScaleWarp = 10;
 // Register redistribution. The block starts at kLaunchRegs per thread (what ptxas grants 384 threads); the third
 // warpgroup drops to kIdleRegs and the two epilogue warpgroups rise to kEpilogueRegs. The rise BLOCKS until the
 // block's own pool holds enough released registers, so released must cover taken exactly or the kernel hangs.
@@ -53,24 +53,30 @@ struct GemmParams {
     uint32_t m_tiles, n_tiles, kblocks, splits, units;
 };
 
-// Scale staging: the epilogue threads copy the block scales of kScaleChunk K blocks at a time into shared memory
-// (cp.async, two chunks in flight), because a scale load that is consumed one K block later still stalls the drain
-// while the L2 is saturated by the tile traffic.
-constexpr int kScaleChunk = 8;
+// Scale staging (FP8 kernel): a warp of its own copies the block scales of every K block into a ring in shared
+// memory, kScaleSlots K blocks ahead of the epilogue and across tile boundaries. The L2 is saturated by the tile
+// traffic while the kernel runs, so a scale load takes microseconds; anything the epilogue warps themselves wait
+// for shows up in the drain.
+constexpr int kScaleSlots = 16;
+
+struct alignas(16) ScaleSlot {
+    float row[kBM];       // scale of each of this CTA's 128 rows of A for the K block
+    float weight[2][2];   // [epilogue warpgroup][b or gate, up]: weight scale of the warpgroup's columns
+};
 
 struct Shared {
     uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2], drain;
+    uint64_t scale_full[kScaleSlots], scale_empty[kScaleSlots];
     uint32_t tmem_base;
     volatile uint32_t abort;
     volatile uint32_t last;
-    float scale_a[2][kScaleChunk][kEpilogueThreads];           // [buffer][K block of the chunk][thread]: own row's scale
-    float scale_w[kEpilogueThreads / 32][2][2][kScaleChunk];   // [warp][buffer][weight (b|gate, up)][K block]
+    ScaleSlot scales[kScaleSlots];
 };
 
 static_assert(sizeof(Shared) <= kControlBytes, "struct Shared outgrew its shared-memory budget");
 static_assert(kPairSmemBytes <= 227 * 1024 && kSmemBytes <= 227 * 1024, "over the shared memory of one CTA");
 
-enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2 };
+enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2, kRoleScales = 3 };
 
 // Bounded wait: gives up after `wait_ns` (or as soon as another role gave up), records who and where, and returns
 // false. Nothing traps; the block then leaves through the common exit.
@@ -105,20 +111,20 @@ __device__ __forceinline__ float load_scale(const void* base, uint64_t index, bo
     return static_cast<const float*>(base)[index];
 }
 
-// One scale value into shared memory without a register round trip when it is FP32 (4-byte cp.async); E8M0 bytes
-// are loaded, decoded and stored.
-__device__ __forceinline__ void stage_scale(float* dst, const void* base, uint64_t index, bool e8m0) {
-    if (e8m0) {
-        *dst = e8m0_to_f32(static_cast<const uint8_t*>(base)[index]);
-    } else {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_addr(dst)),
-                     "l"(static_cast<const float*>(base) + index)
-                     : "memory");
-    }
+// Four consecutive FP32 scale values (16-byte aligned on both sides) into shared memory; only the first `bytes`
+// bytes are read, the rest of the 16 is filled with zeros.
+__device__ __forceinline__ void copy_scales_async16(float* dst, const void* base, uint64_t index, uint32_t bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_addr(dst)),
+                 "l"(static_cast<const float*>(base) + index), "r"(bytes)
+                 : "memory");
 }
-__device__ __forceinline__ void stage_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int PENDING>
-__device__ __forceinline__ void stage_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+// One FP32 scale value into shared memory without a register round trip (4-byte cp.async).
+__device__ __forceinline__ void copy_scale_async(float* dst, const void* base, uint64_t index) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(ptx::smem_addr(dst)),
+                 "l"(static_cast<const float*>(base) + index)
+                 : "memory");
+}
 
 // The activations return what PyTorch's BF16 CUDA kernels return for the same BF16 input: same expressions in FP32,
 // same libdevice functions, default contraction. The result is rounded to BF16 by the caller.
@@ -181,10 +187,17 @@ __device__ __forceinline__ void write_row(const GemmParams& p, const float2 (&ac
     constexpr int kColumns = GATED ? 64 : 128;
     __nv_bfloat16* out = p.out + (uint64_t)row * p.out_stride;
     const __nv_bfloat16* residual = p.residual ? p.residual + (uint64_t)row * p.residual_stride : nullptr;
+    // Two octets go out as one 32-byte store where the row allows it (a warp's store instruction touches 32 rows, so
+    // what counts is bytes per row and instruction: full 32-byte sectors, half as many requests).
+    const bool wide = (reinterpret_cast<uintptr_t>(out + col0) & 31u) == 0;
+    uint4 held = make_uint4(0, 0, 0, 0);
 #pragma unroll
     for (int j = 0; j < kColumns; j += 8) {
         const uint32_t col = col0 + j;
-        if (col >= p.n) break;  // n % 8 == 0: an octet is inside or outside as a whole
+        if (col >= p.n) {  // n % 8 == 0: an octet is inside or outside as a whole
+            if ((j & 8) && wide) st_global_v4(out + col - 8, held);  // the first half of a pair that will not be completed
+            break;
+        }
         // Bias and residual octets either stay packed (four registers each, unpacked value by value) or are widened
         // to FP32 up front. Which of the two keeps ptxas from spilling inside the K loop differs by instance and was
         // chosen by measurement: packed for the gated tiles, widened for the store tiles.
@@ -224,8 +237,10 @@ __device__ __forceinline__ void write_row(const GemmParams& p, const float2 (&ac
                 y[i] = residual ? __fadd_rn(u, wide_res[i]) : u;
             }
         }
-        st_global_v4(out + col, make_uint4(bf16x2_of(y[0], y[1]), bf16x2_of(y[2], y[3]), bf16x2_of(y[4], y[5]),
-                                           bf16x2_of(y[6], y[7])));
+        const uint4 packed = make_uint4(bf16x2_of(y[0], y[1]), bf16x2_of(y[2], y[3]), bf16x2_of(y[4], y[5]), bf16x2_of(y[6], y[7]));
+        if (!wide) st_global_v4(out + col, packed);
+        else if (j & 8) st_global_v8(out + col - 8, held, packed);
+        else held = packed;
     }
 }
 

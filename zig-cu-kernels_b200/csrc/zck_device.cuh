@@ -146,6 +146,12 @@ __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
 __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// 32 bytes at once (sm_100 has 256-bit global accesses); `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, uint4 lo, uint4 hi) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w),
+                 "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+                 : "memory");
+}
 __device__ __forceinline__ void st_global_v2(void* p, uint2 v) {
     asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
