@@ -7,7 +7,7 @@
 // hardware block-scaling path (that path takes E8M0 only), hence the promotion in CUDA cores.
 //
 // Warp roles (384 threads): 0-7 epilogue (warpgroup g owns TMEM columns g*128..g*128+127; warp w reads lanes
-// 32*(w%4)..), 8 TMA producer, 9 MMA issuer and TMEM owner, 10 block-scale producer (fills a 16-deep ring of
+// 32*(w%4)..), 8 TMA producer, 9 MMA issuer and TMEM owner, 10 block-scale producer (fills a 32-deep ring of
 // per-K-block scales in shared memory), 11 idle. The third warpgroup hands most of its registers to the epilogue
 // warpgroups, which hold 128 accumulators per thread.
 // Shared memory: 4 stages x (A 128x128 + B 256x128 bytes) = 192 KiB in the 128-byte swizzle layout.
@@ -53,7 +53,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             ptx::mbar_init(ptx::smem_addr(&sh->tmem_full[b]), 1);
             ptx::mbar_init(ptx::smem_addr(&sh->tmem_empty[b]), (PAIR ? 2 : 1) * kEpilogueThreads / 32);
         }
-        for (int s = 0; s < kScaleSlots; ++s) {
+        for (int s = 0; s < kScaleRuns; ++s) {
             ptx::mbar_init(ptx::smem_addr(&sh->scale_full[s]), 32);                     // the lanes of the scale warp
             ptx::mbar_init(ptx::smem_addr(&sh->scale_empty[s]), kEpilogueThreads / 32);  // the epilogue warps
         }
@@ -196,10 +196,14 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint64_t row_at = (uint64_t)row0 * p.sa_row + (uint64_t)c.kb0 * p.sa_blk;
             uint64_t weight_at = (uint64_t)weight_tile * (up ? p.su_row : p.sb_row) + (uint64_t)c.kb0 * (up ? p.su_blk : p.sb_blk);
             for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
-                const uint32_t slot = it % kScaleSlots, phase = (it / kScaleSlots) & 1u;
-                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->scale_empty[slot]), phase ^ 1u, p, kRoleScales, slot))) break;
+                const uint32_t slot = it % kScaleSlots, run = slot / kScaleRun, phase = (it / kScaleSlots) & 1u;
+                if (slot % kScaleRun == 0 &&
+                    !(ok = wait_barrier(sh, ptx::smem_addr(&sh->scale_empty[run]), phase ^ 1u, p, kRoleScales, run)))
+                    break;
                 ScaleSlot* target = &sh->scales[slot];
-                const uint32_t full = ptx::smem_addr(&sh->scale_full[slot]);
+                // The run goes to the epilogue with its last K block, or with the last K block of all.
+                const bool hand_over = slot % kScaleRun == kScaleRun - 1 || (i + 1 == c.kb_count && unit + unit_step >= p.units);
+                const uint32_t full = ptx::smem_addr(&sh->scale_full[run]);
                 if (all_f32) {
                     if (packed_rows) {
                         if (live_rows) copy_scales_async16(&target->row[4 * lane], p.scale_a, row_at, 4 * live_rows);
@@ -208,13 +212,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             copy_scale_async(&target->row[4 * lane + r], p.scale_a, row_at + r * p.sa_row);
                     }
                     if (brings_weight) copy_scale_async(&target->weight[wg][up], up ? p.scale_u : p.scale_b, weight_at);
-                    ptx::cp_async_mbar_arrive(full);
+                    if (hand_over) ptx::cp_async_mbar_arrive(full);  // counts every copy this lane has issued so far
                 } else {
                     for (uint32_t r = 0; r < live_rows; ++r)
                         target->row[4 * lane + r] = load_scale(p.scale_a, row_at + r * p.sa_row, p.e8m0_bits & 1u);
                     if (brings_weight)
                         target->weight[wg][up] = load_scale(up ? p.scale_u : p.scale_b, weight_at, p.e8m0_bits & (up ? 4u : 2u));
-                    ptx::mbar_arrive(full);  // release: the stores above are visible to whoever sees the phase end
+                    if (hand_over) ptx::mbar_arrive(full);  // release: this lane's stores are visible to whoever sees the phase end
                 }
                 row_at += p.sa_blk;
                 weight_at += up ? p.su_blk : p.sb_blk;
@@ -242,16 +246,21 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 const uint32_t kb = c.kb0 + i;
                 const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
                 // The K block's scales wait in the ring (the scale warp runs kScaleSlots blocks ahead).
-                const uint32_t slot = it % kScaleSlots;
-                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->scale_full[slot]), (it / kScaleSlots) & 1u, p, kRoleEpilogue, 0x10000u + kb))) break;
+                // The product of the K block and, at the start of a run of scales, the run (one wait for both: a second
+                // copy of the give-up logic in this loop made ptxas spill inside it).
+                const uint32_t slot = it % kScaleSlots, run = slot / kScaleRun;
+                if (!(ok = wait_barriers(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, slot % kScaleRun == 0,
+                                         ptx::smem_addr(&sh->scale_full[run]), (it / kScaleSlots) & 1u, p, kRoleEpilogue, kb)))
+                    break;
+                ptx::tc_fence_after();
                 const ScaleSlot* scales = &sh->scales[slot];
                 const float sa = scales->row[lane_row];
                 const float f0 = __fmul_rn(sa, scales->weight[group][0]);
                 const float f1 = GATED ? __fmul_rn(sa, scales->weight[group][1]) : f0;
-                __syncwarp();  // every lane has its scales in registers: the slot can go back
-                if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->scale_empty[slot]));
-                if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, p, kRoleEpilogue, kb))) break;
-                ptx::tc_fence_after();
+                if (slot % kScaleRun == kScaleRun - 1) {
+                    __syncwarp();  // every lane has the run's last scales in registers: the run can go back
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->scale_empty[run]));
+                }
                 if (warp_live) {
                     // Drain in four chunks of 32 columns through two register buffers: the loads of chunks 2 and 3
                     // are in flight while chunks 0 and 1 are folded in, and the buffer goes back to the tensor core

@@ -54,10 +54,12 @@ struct GemmParams {
 };
 
 // Scale staging (FP8 kernel): a warp of its own copies the block scales of every K block into a ring in shared
-// memory, kScaleSlots K blocks ahead of the epilogue and across tile boundaries. The L2 is saturated by the tile
-// traffic while the kernel runs, so a scale load takes microseconds; anything the epilogue warps themselves wait
-// for shows up in the drain.
-constexpr int kScaleSlots = 16;
+// memory, up to kScaleSlots K blocks ahead of the epilogue and across tile boundaries. The L2 is saturated by the
+// tile traffic while the kernel runs, so a scale load takes microseconds; anything the epilogue warps themselves
+// wait for shows up in the drain. Slots change hands in runs of kScaleRun K blocks: one barrier test and one arrival
+// per run and epilogue warp, because each of those is a chain of shared-memory round trips in front of the drain
+// (one per K block cost 15% of the kernel).
+constexpr int kScaleSlots = 32, kScaleRun = 8, kScaleRuns = kScaleSlots / kScaleRun;
 
 struct alignas(16) ScaleSlot {
     float row[kBM];       // scale of each of this CTA's 128 rows of A for the K block
@@ -66,7 +68,7 @@ struct alignas(16) ScaleSlot {
 
 struct Shared {
     uint64_t full[kPairStages], empty[kPairStages], tmem_full[2], tmem_empty[2], drain;
-    uint64_t scale_full[kScaleSlots], scale_empty[kScaleSlots];
+    uint64_t scale_full[kScaleRuns], scale_empty[kScaleRuns];
     uint32_t tmem_base;
     volatile uint32_t abort;
     volatile uint32_t last;
@@ -76,6 +78,9 @@ struct Shared {
 static_assert(sizeof(Shared) <= kControlBytes, "struct Shared outgrew its shared-memory budget");
 static_assert(kPairSmemBytes <= 227 * 1024 && kSmemBytes <= 227 * 1024, "over the shared memory of one CTA");
 
+// How long a waiting thread may stay parked before it looks at the abort flag and the clock again.
+constexpr uint32_t kParkNs = 20000;
+
 enum Role : uint32_t { kRoleProducer = 0, kRoleMma = 1, kRoleEpilogue = 2, kRoleScales = 3 };
 
 // Bounded wait: gives up after `wait_ns` (or as soon as another role gave up), records who and where, and returns
@@ -84,24 +89,49 @@ __device__ __forceinline__ bool wait_barrier(Shared* sh, uint32_t bar, uint32_t 
                                              uint32_t where) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
     const uint64_t start = ptx::global_timer();
-    for (uint32_t spin = 1;; ++spin) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0) {
-            if (sh->abort) return false;
-            if (ptx::global_timer() - start > p.wait_ns) {
-                sh->abort = 1;
-                // Plain stores to the host-mapped record: the first reporter wins approximately, which is all a
-                // diagnostic needs, and no atomic has to cross the bus.
-                volatile uint32_t* status = p.status;
-                if (status[0] == 0u) {
-                    status[1] = blockIdx.x;
-                    status[2] = where;
-                    status[0] = 1u + role;
-                }
-                status[3] = status[3] + 1u;
-                __threadfence_system();
-                return false;
+    for (;;) {
+        if (ptx::mbar_try_wait_parked(bar, parity, kParkNs)) return true;
+        if (sh->abort) return false;
+        if (ptx::global_timer() - start > p.wait_ns) {
+            sh->abort = 1;
+            // Plain stores to the host-mapped record: the first reporter wins approximately, which is all a
+            // diagnostic needs, and no atomic has to cross the bus.
+            volatile uint32_t* status = p.status;
+            if (status[0] == 0u) {
+                status[1] = blockIdx.x;
+                status[2] = where;
+                status[0] = 1u + role;
             }
+            status[3] = status[3] + 1u;
+            __threadfence_system();
+            return false;
+        }
+    }
+}
+
+// The same for two barriers at once (`also` says whether the second one counts): one inlined copy of the give-up
+// logic where a loop would otherwise carry two.
+__device__ __forceinline__ bool wait_barriers(Shared* sh, uint32_t bar, uint32_t parity, bool also, uint32_t bar2, uint32_t parity2,
+                                              const GemmParams& p, uint32_t role, uint32_t where) {
+    bool first = ptx::mbar_try_wait(bar, parity), second = !also || ptx::mbar_try_wait(bar2, parity2);
+    if (first && second) return true;
+    const uint64_t start = ptx::global_timer();
+    for (;;) {
+        if (!first) first = ptx::mbar_try_wait_parked(bar, parity, kParkNs);
+        if (first && !second) second = ptx::mbar_try_wait_parked(bar2, parity2, kParkNs);
+        if (first && second) return true;
+        if (sh->abort) return false;
+        if (ptx::global_timer() - start > p.wait_ns) {
+            sh->abort = 1;
+            volatile uint32_t* status = p.status;
+            if (status[0] == 0u) {
+                status[1] = blockIdx.x;
+                status[2] = first ? (0x10000u | where) : where;  // bit 16: the second barrier is the one that never came
+                status[0] = 1u + role;
+            }
+            status[3] = status[3] + 1u;
+            __threadfence_system();
+            return false;
         }
     }
 }

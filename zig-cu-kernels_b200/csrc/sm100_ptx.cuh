@@ -46,6 +46,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
+// The same test, but the hardware may park the thread for up to `hint_ns` while the phase is still open (it wakes
+// when the phase completes). A parked warp issues nothing, so a long wait does not take issue slots from the warps
+// that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return done != 0;
+}
+
 // ---- TMA ------------------------------------------------------------------------------------------------------
 // 2-D tile load into this CTA's shared memory; completion is counted in bytes on `bar`. `x` (the innermost
 // coordinate) times the element size must be a multiple of 16 bytes.
