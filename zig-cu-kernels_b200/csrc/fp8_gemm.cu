@@ -234,23 +234,25 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
-            const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
-            const uint32_t row = c.m0 + lane_row;
-            const bool row_live = row < p.m;
-            const bool warp_live = c.m0 + quarter * 32 < p.m;
-            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);  // first output column of this thread
+            // Only what the K loop itself needs stays live across it (the epilogue's registers are all spoken for:
+            // 128 accumulators and 64 products in flight); the tile's coordinates are worked out again after it.
+            uint32_t kb_count;
+            bool warp_live;
+            {
+                const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
+                kb_count = c.kb_count;
+                warp_live = c.m0 + quarter * 32 < p.m;
+            }
             float2 acc[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
-            for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
-                const uint32_t kb = c.kb0 + i;
+            for (uint32_t i = 0; i < kb_count; ++i, ++it) {
                 const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
-                // The K block's scales wait in the ring (the scale warp runs kScaleSlots blocks ahead).
                 // The product of the K block and, at the start of a run of scales, the run (one wait for both: a second
                 // copy of the give-up logic in this loop made ptxas spill inside it).
                 const uint32_t slot = it % kScaleSlots, run = slot / kScaleRun;
                 if (!(ok = wait_barriers(sh, ptx::smem_addr(&sh->tmem_full[buf]), use, slot % kScaleRun == 0,
-                                         ptx::smem_addr(&sh->scale_full[run]), (it / kScaleSlots) & 1u, p, kRoleEpilogue, kb)))
+                                         ptx::smem_addr(&sh->scale_full[run]), (it / kScaleSlots) & 1u, p, kRoleEpilogue, it)))
                     break;
                 ptx::tc_fence_after();
                 const ScaleSlot* scales = &sh->scales[slot];
@@ -304,6 +306,10 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 }
             }
             if (!ok) break;
+            const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
+            const uint32_t row = c.m0 + lane_row;
+            const bool row_live = row < p.m;
+            const uint32_t col0 = c.n0 + group * (GATED ? 64 : 128);  // first output column of this thread
             if constexpr (!SPLIT) {
                 if (row_live) write_row_any<GATED, ACT>(p, acc, row, col0);
             } else {
