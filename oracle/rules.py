@@ -275,6 +275,19 @@ def fused_add_rms_norm(x, residual, weight, eps=1e-6, zero_centered=False, out_d
     return rms_norm(h, weight, zero_centered, eps, out_dtype), h
 
 
+def rms_norm_fp8_quant(h, weight, zero_centered=False, eps=1e-6, scale_dtype=torch.float32):
+    """`(codes, scales)` of `rms_norm_fp8_quant(..., fp8_scaling="block128")`: the row quantizer's rules applied to the
+    BF16 result of the norm. tests/test_rms_norm.py:176-191 (`quantize`), :445-457 (`queue_fp8_checks`: codes and scales
+    equal the quantized BF16 reference bit for bit); kernel zig/rms_norm.zig:551-615."""
+    return quantize_rows(rms_norm(h, weight, zero_centered, eps, out_dtype=BF16), scale_dtype)
+
+
+def fused_add_rms_norm_fp8_quant(x, residual, weight, eps=1e-6, zero_centered=False, scale_dtype=torch.float32):
+    """`(codes, scales, h)`. src/zig_cu_kernels/torch/rms_norm.py:509-518."""
+    h = x + residual
+    return (*rms_norm_fp8_quant(h, weight, zero_centered, eps, scale_dtype), h)
+
+
 # --------------------------------------------------------------------------------------------------------------------
 # Tensor-parallel MLP (new work on top of the five ops; the unsharded composition is the oracle)
 # --------------------------------------------------------------------------------------------------------------------

@@ -201,6 +201,30 @@ def norm_vectors(ref, out):
     out["norm_cases"] = np.array(index)
 
 
+def norm_quant_vectors(ref, out):
+    """Block-scaled FP8 outputs of the norm: the reference test's `quantize` applied to its BF16 `norm_pytorch`
+    result (tests/test_rms_norm.py:445-457), for FP32 and E8M0 scales."""
+    generator = torch.Generator().manual_seed(7)
+    index = 0
+    for width in (128, 384, 2048):
+        for rows in (1, 13):
+            x = (torch.randn(rows, width, generator=generator) * 2).bfloat16()
+            other = (torch.randn(rows, width, generator=generator) * 2).bfloat16()
+            if rows > 1:
+                x[rows // 2] = 0
+                other[rows // 2] = 0
+                x[1, :128] *= 2.0 ** -20  # a group of tiny values next to ordinary ones
+            w_bf16 = (torch.randn(width, generator=generator) * 0.5 + 1).bfloat16()
+            h = x + other
+            v = ref["norm_pytorch"](h, w_bf16, False).bfloat16()
+            out[f"nq{index}_x"], out[f"nq{index}_other"], out[f"nq{index}_w"] = raw(x), raw(other), raw(w_bf16)
+            for name, scale_dtype in (("f32", torch.float32), ("e8m0", E8M0)):
+                codes, scales = ref["quantize"](v, "block128", scale_dtype)
+                out[f"nq{index}_codes_{name}"], out[f"nq{index}_scales_{name}"] = raw(codes), raw(scales)
+            index += 1
+    out["nq_cases"] = np.array(index)
+
+
 def main():
     root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
     sys.path[:0] = [str(root / "src"), str(root / "tests")]
@@ -214,13 +238,15 @@ def main():
     ref = functions_of(root / "tests" / "test_fp8_gemm.py", gemm_names,
                        {"torch": torch, "math": math, "FP8": FP8, "E8M0": E8M0, "SCALE_GROUP": GROUP,
                         "FUNCTIONS": functions})
-    norm = functions_of(root / "tests" / "test_rms_norm.py", {"norm_pytorch", "norm_exact", "fp32"},
-                        {"torch": torch, "np": np, "BF16": torch.bfloat16, "EPS": 1e-6})
+    norm = functions_of(root / "tests" / "test_rms_norm.py", {"norm_pytorch", "norm_exact", "fp32", "quantize", "e8m0_bytes"},
+                        {"torch": torch, "np": np, "BF16": torch.bfloat16, "EPS": 1e-6, "FP8": FP8, "E8M0": E8M0,
+                         "FP8_MAX": 448.0})
     quant, gemm, norms = {}, {}, {}
     quantizer_vectors(ref, quant)
     config1_vectors(ref, references, packs, gemm)
     epilogue_vectors(ref, gemm)
     norm_vectors(norm, norms)
+    norm_quant_vectors(norm, norms)
     np.savez_compressed(HERE / "quantizers.npz", **quant)
     np.savez_compressed(HERE / "gemm.npz", **gemm)
     np.savez_compressed(HERE / "norm.npz", **norms)

@@ -177,3 +177,107 @@ def test_empty_inputs_and_errors(ops):
         ops.rms_norm(x, None, torch.tensor(1e-6))
     with pytest.raises(OverflowError):
         ops.rms_norm(x, None, 1e39)
+
+
+# ---- rms_norm_fp8_quant / fused_add_rms_norm_fp8_quant, block128 (the reference's tests/test_rms_norm.py:445-472:
+# codes and scales equal the quantizer's rules applied to the BF16 result of the same norm, bit for bit) ------------
+
+E8M0 = torch.float8_e8m0fnu
+BLOCK_WIDTHS = [128, 256, 384, 1024, 2048, 4096, 8192, 16384, 32768]
+
+
+@pytest.mark.parametrize("scale_dtype", [F32, E8M0])
+@pytest.mark.parametrize("x_dtype,weight_dtype,zero_centered", [(BF16, BF16, False), (BF16, None, False),
+                                                                (BF16, F32, True), (F32, BF16, False)])
+def test_block_quantized_outputs_quantize_the_bf16_result(ops, x_dtype, weight_dtype, zero_centered, scale_dtype):
+    torch.manual_seed(3)
+    for width in BLOCK_WIDTHS:
+        if width * (2 if x_dtype == BF16 else 4) > 131072:
+            continue
+        for rows in (1, 6, 13, 67):
+            x = (torch.randn(rows, width, device="cuda") * 3).to(x_dtype)
+            other = (torch.randn(rows, width, device="cuda") * 3).to(x_dtype)
+            if rows > 1:
+                x[rows // 2] = 0
+                other[rows // 2] = 0
+                x[1, :128] *= 2.0**-20
+                other[1, :128] *= 2.0**-20
+            weight = None if weight_dtype is None else (torch.randn(width, device="cuda") * 0.5 + 1).to(weight_dtype)
+            # plain
+            v = ops.rms_norm(x, weight, EPS, zero_centered=zero_centered, out_dtype=BF16)
+            q, scales = ops.rms_norm_fp8_quant(x, weight, EPS, fp8_scaling="block128", fp8_scale_dtype=scale_dtype,
+                                               zero_centered=zero_centered)
+            codes, expected = rules.quantize_rows(v.cpu(), scale_dtype)
+            assert_same_bits(q.cpu(), codes, f"codes {width}x{rows}")
+            assert_same_bits(scales.cpu(), expected, f"scales {width}x{rows}")
+            assert scales.stride() == (1, rows) or scales.shape[1] == 1
+            q2, scales2 = ops.quantize_fp8_rows(v, scale_dtype=scale_dtype)
+            assert_same_bits(q.cpu(), q2.cpu(), "codes vs quantize_fp8_rows")
+            assert_same_bits(scales.cpu(), scales2.cpu(), "scales vs quantize_fp8_rows")
+            # fused add
+            v, h = ops.fused_add_rms_norm(x, other, weight, EPS, zero_centered=zero_centered, out_dtype=BF16)
+            q, scales, h2 = ops.fused_add_rms_norm_fp8_quant(x, other, weight, EPS, fp8_scaling="block128",
+                                                             fp8_scale_dtype=scale_dtype, zero_centered=zero_centered)
+            codes, expected = rules.quantize_rows(v.cpu(), scale_dtype)
+            assert_same_bits(q.cpu(), codes, f"fused codes {width}x{rows}")
+            assert_same_bits(scales.cpu(), expected, f"fused scales {width}x{rows}")
+            assert_same_bits(h2.cpu(), h.cpu(), "residual_out")
+
+
+def test_block_quantized_golden_rows(ops, golden):
+    """On the golden inputs the fused op stays within the quantizer's rules of ITS norm; where the norm has the bits of
+    the PyTorch sequence (the golden one) the codes are the golden codes."""
+    g = golden["norm"]
+    for index in range(int(g["nq_cases"])):
+        x, other = from_golden(g[f"nq{index}_x"], BF16).cuda(), from_golden(g[f"nq{index}_other"], BF16).cuda()
+        w = from_golden(g[f"nq{index}_w"], BF16).cuda()
+        v, _ = ops.fused_add_rms_norm(x, other, w, EPS)
+        golden_v = rules.rms_norm((x + other).cpu(), w.cpu())
+        for name, scale_dtype in (("f32", F32), ("e8m0", E8M0)):
+            q, scales, _ = ops.fused_add_rms_norm_fp8_quant(x, other, w, EPS, fp8_scaling="block128",
+                                                            fp8_scale_dtype=scale_dtype)
+            rows_equal = same_bits(v.cpu(), golden_v).reshape(v.shape[0], -1, 128).all(-1)  # per (row, group)
+            got = same_bits(q.cpu(), from_golden(g[f"nq{index}_codes_{name}"], FP8)).reshape(v.shape[0], -1, 128).all(-1)
+            assert bool((got | ~rows_equal).all()), "a group whose norm has the golden bits has other codes"
+            assert float(rows_equal.float().mean()) > 0.5
+
+
+def test_block_quantized_out_variants_and_errors(ops):
+    torch.manual_seed(5)
+    rows, width = 9, 512
+    x = torch.randn(rows, width, device="cuda", dtype=BF16)
+    other = torch.randn(rows, width, device="cuda", dtype=BF16)
+    w = torch.randn(width, device="cuda", dtype=BF16)
+    q, scales, h = ops.fused_add_rms_norm_fp8_quant(x, other, w, EPS, fp8_scaling="block128")
+    # row-major scales_out, strided codes, residual_out aliasing residual
+    scales_out = torch.empty(rows, width // 128, device="cuda")
+    wide = torch.empty(rows, 2 * width, device="cuda", dtype=FP8)
+    residual = other.clone()
+    got = ops.fused_add_rms_norm_fp8_quant(x, residual, w, EPS, fp8_scaling="block128", out=wide[:, :width],
+                                           scales_out=scales_out, residual_out=residual)
+    assert got[0].data_ptr() == wide.data_ptr() and got[1] is scales_out and got[2] is residual
+    assert_same_bits(wide[:, :width].cpu(), q.cpu(), "strided codes")
+    assert_same_bits(scales_out.cpu(), scales.cpu(), "row-major scales")
+    assert_same_bits(residual.cpu(), h.cpu(), "residual in place")
+    # leading dimensions
+    q3, s3 = ops.rms_norm_fp8_quant(x.reshape(3, 3, width), w, EPS, fp8_scaling="block128")
+    q1, s1 = ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="block128")
+    assert q3.shape == (3, 3, width) and s3.shape == (rows, width // 128)
+    assert_same_bits(q3.reshape(rows, width).cpu(), q1.cpu(), "leading dims")
+    # tensorwise goes through the given scale
+    scale = torch.tensor([0.0123], device="cuda")
+    qt, st = ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="tensorwise", fp8_scale=scale)
+    assert st.data_ptr() == scale.data_ptr() and qt.dtype == FP8
+    with pytest.raises(NotImplementedError):
+        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="rowwise")
+    with pytest.raises(ValueError):
+        ops.rms_norm_fp8_quant(x[:, :264], w[:264], EPS, fp8_scaling="block128")
+    with pytest.raises(ValueError):
+        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="block128", fp8_scale=scale)
+    with pytest.raises(ValueError):
+        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="tensorwise")
+    with pytest.raises(ValueError):
+        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="nope")
+    # empty
+    q0, s0 = ops.rms_norm_fp8_quant(x[:0], w, EPS, fp8_scaling="block128")
+    assert q0.shape == (0, width) and s0.shape == (0, width // 128)

@@ -158,3 +158,18 @@ def test_c_restatement_matches_the_reference_vectors(golden):
             got = scales.view(E8M0) if scale_dtype == E8M0 else scales
             assert_same_bits(got, from_golden(g[f"tiles{n}_scales_f32_{stag}"], scale_dtype), f"C tile scales {n} {stag}")
             assert_same_bits(codes.view(FP8), from_golden(g[f"tiles{n}_codes_f32_{stag}"], FP8), f"C tile codes {n} {stag}")
+
+
+def test_norm_block_quantized_outputs_match_the_reference(golden):
+    """`rms_norm_fp8_quant(block128)` of the oracle = the reference test's `quantize` of its BF16 norm, bit for bit."""
+    g = golden["norm"]
+    E8M0 = torch.float8_e8m0fnu
+    assert int(g["nq_cases"]) == 6
+    for index in range(int(g["nq_cases"])):
+        x, other = from_golden(g[f"nq{index}_x"], BF16), from_golden(g[f"nq{index}_other"], BF16)
+        w = from_golden(g[f"nq{index}_w"], BF16)
+        for name, scale_dtype in (("f32", torch.float32), ("e8m0", E8M0)):
+            codes, scales, h = rules.fused_add_rms_norm_fp8_quant(x, other, w, scale_dtype=scale_dtype)
+            assert_same_bits(codes, from_golden(g[f"nq{index}_codes_{name}"], FP8), f"codes {name}")
+            assert_same_bits(scales, from_golden(g[f"nq{index}_scales_{name}"], scale_dtype), f"scales {name}")
+            assert_same_bits(h, x + other, "h")

@@ -5,6 +5,10 @@
 // squares is reduced by warp shuffles and, for rows wider than a warp, one shared-memory exchange; then
 // y = weight (*) kind_of_x(h * rsqrt(mean + eps)).
 //
+// With block scales (zck_fused_add_rms_norm_quant) the BF16 result is not stored: the 16 (BF16 x) or 32 (FP32 x) lanes
+// that hold a group of 128 values agree on its absmax by shuffles and store E4M3 codes and one scale per group, the
+// same bits as the row quantizer gives for the BF16 result.
+//
 // T and C depend on the row width only, never on the row count, so a row gets the same reduction tree in every
 // batch (batch invariance). Algorithmic traffic per row of d BF16 values: 2 reads + 2 writes of 2d bytes, + 2d of
 // weight (L2 resident).
@@ -20,6 +24,8 @@ struct NormArgs {
     const void* weight;
     const float* fp8_scale;
     void* y;
+    void* scales;           // block scales (y_kind kBlockF32 / kBlockE8M0): scales[group * scale_stride + row]
+    uint64_t scale_stride;
     uint64_t x_stride, r_stride, ro_stride, y_stride;
     uint32_t rows, width, chunks;  // chunks = width / values per 16-byte chunk of x
     uint32_t threads_per_row;      // T
@@ -104,6 +110,51 @@ __device__ __forceinline__ void store_y(void* y, int y_kind, uint64_t offset, co
     }
 }
 
+// Internal output kinds next to ZCK_BF16 / ZCK_F32 / ZCK_FP8_E4M3: E4M3 codes with one computed scale per 128 values.
+constexpr int kBlockF32 = 16, kBlockE8M0 = 17;
+
+// Codes and scale of the V values `v` of one chunk whose group of 128 spans LANES consecutive lanes.
+template <int V, int LANES>
+__device__ __forceinline__ void store_block_quantized(const NormArgs& a, uint64_t row, uint32_t chunk, float (&v)[V],
+                                                      bool live) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        v[i] = bf16_round(v[i]);  // what is quantized is the BF16 result
+        amax = max_nan(amax, abs_f32(v[i]));
+    }
+    amax = max_nan_over_lanes<LANES>(amax);
+    const bool e8m0 = a.y_kind == kBlockE8M0;
+    const uint32_t group = chunk / LANES;
+    float q[V];
+    if (e8m0) {
+        const uint32_t byte = scale_e8m0_of(amax);
+        const float factor = e8m0_reciprocal(byte);
+#pragma unroll
+        for (int i = 0; i < V; ++i) q[i] = __fmul_rn(v[i], factor);
+        if (live && chunk % LANES == 0) static_cast<uint8_t*>(a.scales)[(uint64_t)group * a.scale_stride + row] = (uint8_t)byte;
+    } else {
+        const float scale = scale_f32_of(amax);
+        const GroupDivider divide = GroupDivider::of(scale);
+        if (divide.fast) {
+#pragma unroll
+            for (int i = 0; i < V; i += 2) {
+                const float2 two = divide.corrected(v[i], v[i + 1]);
+                q[i] = two.x;
+                q[i + 1] = two.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < V; ++i) q[i] = __fdiv_rn(v[i], scale);
+        }
+        if (live && chunk % LANES == 0) static_cast<float*>(a.scales)[(uint64_t)group * a.scale_stride + row] = scale;
+    }
+    if (!live) return;
+    uint8_t* p = static_cast<uint8_t*>(a.y) + row * a.y_stride + (uint64_t)chunk * V;
+    if (V == 8) st_global_v2(p, make_uint2(e4m3x4_of(q[0], q[1], q[2], q[3]), e4m3x4_of(q[V - 4], q[V - 3], q[V - 2], q[V - 1])));
+    else *reinterpret_cast<uint32_t*>(p) = e4m3x4_of(q[0], q[1], q[2], q[3]);
+}
+
 constexpr int kMinBlock = 128;
 
 // Threads per block by instance: rows of up to 128 threads share blocks of 128; C == 8 rows take up to 512 threads
@@ -176,10 +227,14 @@ __global__ void __launch_bounds__(max_block<XT, C>()) rms_norm_kernel(const Norm
     const float fp8_scale = a.y_kind == ZCK_FP8_E4M3 ? __ldg(a.fp8_scale) : 1.0f;
     const bool zero_centered = (a.weight_kind & ZCK_WEIGHT_ZERO_CENTERED) != 0;
     const int weight = a.weight_kind & 3;
-    if (!live) return;
+    const bool blocks = a.y_kind >= kBlockF32;
+    if (!live && !blocks) return;  // with block scales every lane of a warp stays for the shuffles
 #pragma unroll
     for (int c = 0; c < C; ++c) {
         uint32_t chunk = c * T + t;
+        // Block scales: groups are whole (width % 128 == 0), so the lanes of a group are all in or all out, and a
+        // warp-uniform test keeps the shuffles converged (T >= 32: one row per warp; T == 16: two rows per warp
+        // with the same chunk index).
         if (chunk >= a.chunks) continue;
         float y[V];
         Chunk<XT>::unpack(held[c], y);
@@ -200,7 +255,8 @@ __global__ void __launch_bounds__(max_block<XT, C>()) rms_norm_kernel(const Norm
                 for (int i = 0; i < V; ++i) y[i] = __fmul_rn(w[i], y[i]);
             }
         }
-        store_y<V>(a.y, a.y_kind, row * a.y_stride + (uint64_t)chunk * V, y, fp8_scale);
+        if (blocks) store_block_quantized<V, 128 / V>(a, row, chunk, y, live);
+        else store_y<V>(a.y, a.y_kind, row * a.y_stride + (uint64_t)chunk * V, y, fp8_scale);
     }
 }
 
@@ -240,17 +296,21 @@ static cudaError_t launch_norm(const NormArgs& a, int c, cudaStream_t stream) {
 
 using namespace zck;
 
-extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stride, const void* residual,
-                                      uint64_t r_stride, void* residual_out, uint64_t ro_stride, const void* weight,
-                                      int weight_kind, const float* fp8_scale, void* y, int y_kind, uint64_t y_stride,
-                                      uint32_t rows, uint32_t width, float eps, int device, void* stream) {
+static int norm_entry(const void* x, int x_kind, uint64_t x_stride, const void* residual, uint64_t r_stride,
+                      void* residual_out, uint64_t ro_stride, const void* weight, int weight_kind, const float* fp8_scale,
+                      void* y, int y_kind, uint64_t y_stride, void* scales, uint64_t scale_stride, uint32_t rows,
+                      uint32_t width, float eps, int device, void* stream) {
     if (rows == 0 || width == 0) return ZCK_OK;
+    const bool blocks = y_kind >= kBlockF32;
     ZCK_REQUIRE(x_kind == ZCK_BF16 || x_kind == ZCK_F32, "x must be BF16 or FP32");
-    ZCK_REQUIRE(y_kind == ZCK_BF16 || y_kind == ZCK_F32 || y_kind == ZCK_FP8_E4M3, "y must be BF16, FP32 or E4M3");
+    ZCK_REQUIRE(blocks || y_kind == ZCK_BF16 || y_kind == ZCK_F32 || y_kind == ZCK_FP8_E4M3, "y must be BF16, FP32 or E4M3");
     ZCK_REQUIRE(width % 8 == 0, "the row length must be a multiple of 8, got %u", width);
+    ZCK_REQUIRE(!blocks || width % kGroup == 0, "block scales need a row length that is a multiple of 128, got %u", width);
     uint32_t x_bytes = x_kind == ZCK_BF16 ? 2 : 4;
     ZCK_REQUIRE((uint64_t)width * x_bytes <= 131072, "rows of %u values are too wide for this kernel", width);
     ZCK_REQUIRE(x && y, "x and y must not be NULL");
+    ZCK_REQUIRE(!blocks || scales, "scales must not be NULL");
+    ZCK_REQUIRE(!blocks || y_kind == kBlockE8M0 || aligned(scales, 4), "FP32 scales must start at a multiple of 4 bytes");
     ZCK_REQUIRE((residual == nullptr) == (residual_out == nullptr), "residual and residual_out go together");
     int weight_base = weight_kind & 3;
     ZCK_REQUIRE(weight_base <= ZCK_WEIGHT_F32 && (weight_kind & ~7) == 0, "unknown weight kind %d", weight_kind);
@@ -258,7 +318,7 @@ extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stri
     ZCK_REQUIRE(!(weight_kind & ZCK_WEIGHT_ZERO_CENTERED) || weight, "zero_centered needs a weight");
     ZCK_REQUIRE((y_kind == ZCK_FP8_E4M3) == (fp8_scale != nullptr), "fp8_scale goes with an E4M3 output only");
     uint32_t y_bytes = y_kind == ZCK_BF16 ? 2 : y_kind == ZCK_F32 ? 4 : 1;
-    uint32_t y_align = y_kind == ZCK_FP8_E4M3 ? (x_kind == ZCK_BF16 ? 8 : 4) : 16;
+    uint32_t y_align = y_bytes == 1 ? (x_kind == ZCK_BF16 ? 8 : 4) : 16;
     if (y_kind == ZCK_BF16 && x_kind == ZCK_F32) y_align = 8;
     ZCK_REQUIRE(aligned(x, 16) && (rows <= 1 || x_stride * x_bytes % 16 == 0), "x needs 16-byte aligned rows");
     ZCK_REQUIRE(aligned(y, y_align) && (rows <= 1 || y_stride * y_bytes % y_align == 0), "y needs %u-byte aligned rows",
@@ -275,6 +335,7 @@ extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stri
     ZCK_CUDA(guard.error);
     NormArgs a;
     a.x = x; a.residual = residual; a.residual_out = residual_out; a.weight = weight; a.fp8_scale = fp8_scale; a.y = y;
+    a.scales = scales; a.scale_stride = scale_stride;
     a.x_stride = x_stride; a.r_stride = r_stride; a.ro_stride = ro_stride; a.y_stride = y_stride;
     a.rows = rows; a.width = width; a.chunks = width * x_bytes / 16;
     a.weight_kind = weight_kind; a.y_kind = y_kind; a.eps = eps;
@@ -287,4 +348,23 @@ extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stri
     else error = residual ? launch_norm<float, true>(a, c, s) : launch_norm<float, false>(a, c, s);
     if (error != cudaSuccess) return fail(ZCK_ERR_CUDA, "rms_norm launch failed: %s", cudaGetErrorString(error));
     return ZCK_OK;
+}
+
+extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stride, const void* residual,
+                                      uint64_t r_stride, void* residual_out, uint64_t ro_stride, const void* weight,
+                                      int weight_kind, const float* fp8_scale, void* y, int y_kind, uint64_t y_stride,
+                                      uint32_t rows, uint32_t width, float eps, int device, void* stream) {
+    ZCK_REQUIRE(y_kind == ZCK_BF16 || y_kind == ZCK_F32 || y_kind == ZCK_FP8_E4M3, "y must be BF16, FP32 or E4M3");
+    return norm_entry(x, x_kind, x_stride, residual, r_stride, residual_out, ro_stride, weight, weight_kind, fp8_scale, y,
+                      y_kind, y_stride, nullptr, 0, rows, width, eps, device, stream);
+}
+
+extern "C" int zck_fused_add_rms_norm_quant(const void* x, int x_kind, uint64_t x_stride, const void* residual,
+                                            uint64_t r_stride, void* residual_out, uint64_t ro_stride,
+                                            const void* weight, int weight_kind, void* codes, uint64_t codes_stride,
+                                            void* scales, uint64_t scale_stride, int scale_is_e8m0, uint32_t rows,
+                                            uint32_t width, float eps, int device, void* stream) {
+    return norm_entry(x, x_kind, x_stride, residual, r_stride, residual_out, ro_stride, weight, weight_kind, nullptr, codes,
+                      scale_is_e8m0 ? kBlockE8M0 : kBlockF32, codes_stride, scales, scale_stride, rows, width, eps, device,
+                      stream);
 }

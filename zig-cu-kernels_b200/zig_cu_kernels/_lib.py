@@ -44,6 +44,8 @@ SIGNATURES = {
                                               ctypes.c_int, ptr]),
     "zck_fused_add_rms_norm": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, u64, ptr, u64, ptr, ctypes.c_int, ptr, ptr,
                                               ctypes.c_int, u64, u32, u32, ctypes.c_float, ctypes.c_int, ptr]),
+    "zck_fused_add_rms_norm_quant": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, u64, ptr, u64, ptr, ctypes.c_int, ptr, u64,
+                                                    ptr, u64, ctypes.c_int, u32, u32, ctypes.c_float, ctypes.c_int, ptr]),
     "zck_gemm_plan": (ctypes.c_int, [ctypes.POINTER(GemmSizes), ctypes.c_int, ctypes.c_int,
                                      ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(u32)]),
     "zck_fp8_gemm": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes),

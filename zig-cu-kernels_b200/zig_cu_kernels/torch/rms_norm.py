@@ -1,4 +1,4 @@
-"""`rms_norm` and `fused_add_rms_norm` as PyTorch custom ops over libzck_b200.
+"""`rms_norm`, `fused_add_rms_norm` and their `_fp8_quant` forms as PyTorch custom ops over libzck_b200.
 
 Same schemas, aliasing rules and rounding points as the reference's src/zig_cu_kernels/torch/rms_norm.py (`rms_norm`
 :486-488, `fused_add_rms_norm` :428-429, :491-496, `run` :328-370): `h = x + residual` rounded once to the dtype of `x`
@@ -6,6 +6,11 @@ and returned as `residual_out`; `y = weight * dtype_of_x(h * rsqrt(mean(h^2) + e
 weight, `weight * (h * r)` for an FP32 weight, `(h * r) * (1 + weight)` when zero-centered. Outputs may be the exact
 views `x` or `residual`; any other overlap goes through a temporary. The launch shape depends on the row width only,
 so results do not depend on the batch.
+
+`rms_norm_fp8_quant` / `fused_add_rms_norm_fp8_quant` (reference :499-518, ops :432-434): the BF16 result is quantized
+in the same pass. `fp8_scaling="tensorwise"` takes the caller's one-element `fp8_scale`; `"block128"` computes one
+scale per row and 128 values and returns `(q, scales[, residual_out])` with the bits of `quantize_fp8_rows(norm)`;
+`"rowwise"` is part of the reference's surface and not built here.
 """
 
 import math
@@ -13,13 +18,15 @@ import math
 import torch
 
 from .. import _lib
-from .common import KINDS, need_choice, need_dtype, raw_stream, row_matrix, writes_in_place
+from .common import GROUP, KINDS, block_scales_like, need_choice, need_dtype, raw_stream, row_matrix, writes_in_place
 from .ops import Out, Param, define
 
-__all__ = ["rms_norm", "fused_add_rms_norm", "rms_norm_op", "rms_norm_out_op", "fused_add_rms_norm_op",
-           "fused_add_rms_norm_out_op"]
+__all__ = ["rms_norm", "fused_add_rms_norm", "rms_norm_fp8_quant", "fused_add_rms_norm_fp8_quant", "rms_norm_op",
+           "rms_norm_out_op", "fused_add_rms_norm_op", "fused_add_rms_norm_out_op", "rms_norm_fp8_quant_op",
+           "rms_norm_fp8_quant_out_op", "fused_add_rms_norm_fp8_quant_op", "fused_add_rms_norm_fp8_quant_out_op"]
 
-BF16, F32, FP8 = torch.bfloat16, torch.float32, torch.float8_e4m3fn
+BF16, F32, FP8, E8M0 = torch.bfloat16, torch.float32, torch.float8_e4m3fn, torch.float8_e8m0fnu
+COMPUTED_SCALINGS = ("rowwise", "block128")
 X_DTYPES = (BF16, F32)
 MAX_ROW_BYTES = 131072
 LIMIT_32 = (1 << 32) - 1
@@ -84,12 +91,15 @@ def y_alignment(x, out):
     return min(16, values * out.element_size())
 
 
-def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_out):
+def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_out, scales_out=None):
+    """Queues one launch. With `scales_out` (block128 scales, `(rows, width/128)`) `out` holds E4M3 codes."""
     if tuple(out.shape) != tuple(x.shape):
         raise ValueError(f"out must have the shape {tuple(x.shape)}, got {tuple(out.shape)}")
     if residual_out is not None and tuple(residual_out.shape) != tuple(x.shape):
         raise ValueError(f"residual_out must have the shape {tuple(x.shape)}, got {tuple(residual_out.shape)}")
     rows, width = math.prod(x.shape[:-1]), x.shape[-1]
+    if scales_out is not None and tuple(scales_out.shape) != (rows, width // GROUP):
+        raise ValueError(f"scales_out must have the shape {(rows, width // GROUP)}, got {tuple(scales_out.shape)}")
     if rows == 0 or width == 0:
         return
     # Inputs the kernel cannot address in place are copied once.
@@ -118,14 +128,30 @@ def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_o
         weight_kind = (_lib.WEIGHT_BF16 if weight.dtype == BF16 else _lib.WEIGHT_F32) | (
             _lib.WEIGHT_ZERO_CENTERED if zero_centered else 0)
     device = x.get_device()
-    _lib.check(_lib.library().zck_fused_add_rms_norm(
-        x_in.data_ptr(), KINDS[x.dtype], rows_for_kernel(x_in, 16),
-        None if r_in is None else r_in.data_ptr(), 0 if r_in is None else rows_for_kernel(r_in, 16),
-        None if h_target is None else h_target.data_ptr(),
-        0 if h_target is None else rows_for_kernel(h_target, 16, output=True),
-        None if w_in is None else w_in.data_ptr(), weight_kind, None if s_in is None else s_in.data_ptr(),
-        y_target.data_ptr(), KINDS[out.dtype], rows_for_kernel(y_target, y_alignment(x, out), output=True),
-        rows, width, float(eps), device, raw_stream(device)))
+    leading = (x_in.data_ptr(), KINDS[x.dtype], rows_for_kernel(x_in, 16),
+               None if r_in is None else r_in.data_ptr(), 0 if r_in is None else rows_for_kernel(r_in, 16),
+               None if h_target is None else h_target.data_ptr(),
+               0 if h_target is None else rows_for_kernel(h_target, 16, output=True),
+               None if w_in is None else w_in.data_ptr(), weight_kind)
+    y_stride = rows_for_kernel(y_target, y_alignment(x, out), output=True)
+    if scales_out is None:
+        _lib.check(_lib.library().zck_fused_add_rms_norm(
+            *leading, None if s_in is None else s_in.data_ptr(), y_target.data_ptr(), KINDS[out.dtype], y_stride,
+            rows, width, float(eps), device, raw_stream(device)))
+    else:
+        # Scales in place when they have the quantizer's layout (rows contiguous, one column per group) and overlap
+        # nothing that is read; otherwise through a temporary of that layout.
+        groups = width // GROUP
+        direct = ((rows <= 1 or scales_out.stride(0) == 1) and (groups <= 1 or scales_out.stride(1) >= rows) and
+                  writes_in_place(scales_out, [*others, *row_inputs]) and
+                  (scales_out.dtype == E8M0 or scales_out.data_ptr() % 4 == 0))
+        scales_target = scales_out if direct else block_scales_like(x, scales_out.dtype)
+        _lib.check(_lib.library().zck_fused_add_rms_norm_quant(
+            *leading, y_target.data_ptr(), y_stride, scales_target.data_ptr(),
+            scales_target.stride(1) if groups > 1 else rows, int(scales_out.dtype == E8M0), rows, width, float(eps),
+            device, raw_stream(device)))
+        if scales_target is not scales_out:
+            scales_out.copy_(scales_target)
     if y_target is not out:
         out.copy_(y_target)
     if h_target is not residual_out:
@@ -190,6 +216,78 @@ FUSED_ADD = define(
 fused_add_rms_norm_op, fused_add_rms_norm_out_op = FUSED_ADD.functional, FUSED_ADD.out
 
 
+# ---- rms_norm_fp8_quant, fused_add_rms_norm_fp8_quant (computed scales) --------------------------------------------
+
+def check_quant(x, residual, weight, zero_centered, fp8_scaling, fp8_scale_dtype):
+    check_common(x, residual, weight, None, zero_centered, None)
+    need_choice("fp8_scaling", fp8_scaling, COMPUTED_SCALINGS)
+    need_choice("fp8_scale_dtype", fp8_scale_dtype, (F32, E8M0) if fp8_scaling == "block128" else (F32,))
+    if fp8_scaling != "block128":
+        raise NotImplementedError(f"fp8_scaling={fp8_scaling!r} is not built in this library yet; only block128 is")
+
+
+def check_quant_sizes(x, residual, weight):
+    check_common_sizes(x, residual, weight, None)
+    if x.shape[-1] % GROUP:
+        raise ValueError(f"fp8_scaling='block128' needs a row length that is a multiple of {GROUP}")
+
+
+def codes_like(x):
+    return x.new_empty(x.shape, dtype=FP8)
+
+
+PLAIN_QUANT = define(
+    "rms_norm_fp8_quant",
+    params=[Param("Tensor", "x"), Param("Tensor?", "weight"), Param("float", "eps"), Param("bool", "zero_centered"),
+            Param("str", "fp8_scaling"), Param("ScalarType", "fp8_scale_dtype")],
+    outs=[Out("out", "out", lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: codes_like(x), FP8),
+          Out("scales_out", "scales_out",
+              lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: block_scales_like(x, fp8_scale_dtype),
+              "fp8_scale_dtype")],
+    check=lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant(
+        x, None, weight, zero_centered, fp8_scaling, fp8_scale_dtype),
+    check_sizes=lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant_sizes(x, None, weight),
+    run=lambda x, weight, eps, zero_centered, fp8_scaling, out, scales_out: run_norm(
+        x, None, weight, None, eps, zero_centered, out, None, scales_out))
+rms_norm_fp8_quant_op, rms_norm_fp8_quant_out_op = PLAIN_QUANT.functional, PLAIN_QUANT.out
+
+FUSED_QUANT = define(
+    "fused_add_rms_norm_fp8_quant",
+    params=[Param("Tensor", "x"), Param("Tensor", "residual"), Param("Tensor?", "weight"), Param("float", "eps"),
+            Param("bool", "zero_centered"), Param("str", "fp8_scaling"), Param("ScalarType", "fp8_scale_dtype")],
+    outs=[Out("out", "out",
+              lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: codes_like(x), FP8),
+          Out("scales_out", "scales_out",
+              lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: block_scales_like(
+                  x, fp8_scale_dtype), "fp8_scale_dtype"),
+          Out("residual_out", "residual_out",
+              lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: x.new_empty(x.shape), "x")],
+    check=lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant(
+        x, residual, weight, zero_centered, fp8_scaling, fp8_scale_dtype),
+    check_sizes=lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant_sizes(
+        x, residual, weight),
+    run=lambda x, residual, weight, eps, zero_centered, fp8_scaling, out, scales_out, residual_out: run_norm(
+        x, residual, weight, None, eps, zero_centered, out, residual_out, scales_out))
+fused_add_rms_norm_fp8_quant_op, fused_add_rms_norm_fp8_quant_out_op = FUSED_QUANT.functional, FUSED_QUANT.out
+
+
+def given_scale(fp8_scaling, fp8_scale, fp8_scale_dtype, scales_out):
+    """Checks the scale arguments of a `_fp8_quant` function; True when the call takes the caller's scale."""
+    if fp8_scaling != "tensorwise":
+        if fp8_scale is not None:
+            raise ValueError(f"fp8_scaling={fp8_scaling!r} computes the scales and takes no fp8_scale")
+        return False
+    if fp8_scale is None:
+        raise ValueError("fp8_scaling='tensorwise' needs fp8_scale")
+    if fp8_scale.numel() != 1:
+        raise ValueError(f"fp8_scale must hold one element, got the shape {tuple(fp8_scale.shape)}")
+    if fp8_scale_dtype != F32:
+        raise ValueError(f"fp8_scaling='tensorwise' takes FP32 scales, got fp8_scale_dtype={fp8_scale_dtype}")
+    if scales_out is not None:
+        raise ValueError("fp8_scaling='tensorwise' returns fp8_scale and takes no scales_out")
+    return True
+
+
 def _resolved(x, out_dtype):
     return getattr(x, "dtype", None) if out_dtype is None else out_dtype
 
@@ -203,3 +301,23 @@ def fused_add_rms_norm(x, residual, weight, eps, *, zero_centered=False, out_dty
     """`(y, residual_out)`: the residual stream `x + residual` and its RMS norm, in one pass over the rows."""
     return FUSED_ADD(x, residual, weight, None, eps, zero_centered, _resolved(x, out_dtype),
                      outputs={"out": out, "residual_out": residual_out})
+
+
+def rms_norm_fp8_quant(x, weight, eps, *, fp8_scaling, fp8_scale=None, fp8_scale_dtype=torch.float32, zero_centered=False,
+                       out=None, scales_out=None):
+    """`(q, scales)`: E4M3 codes of the BF16 RMS norm of `x` and their scales for the scaling type `fp8_scaling`."""
+    if given_scale(fp8_scaling, fp8_scale, fp8_scale_dtype, scales_out):
+        return RMS_NORM(x, weight, fp8_scale, eps, zero_centered, FP8, outputs={"out": out}), fp8_scale.reshape(())
+    return PLAIN_QUANT(x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype,
+                       outputs={"out": out, "scales_out": scales_out})
+
+
+def fused_add_rms_norm_fp8_quant(x, residual, weight, eps, *, fp8_scaling, fp8_scale=None, fp8_scale_dtype=torch.float32,
+                                 zero_centered=False, out=None, scales_out=None, residual_out=None):
+    """`(q, scales, residual_out)`: the results of `fused_add_rms_norm`, quantized as in `rms_norm_fp8_quant`."""
+    if given_scale(fp8_scaling, fp8_scale, fp8_scale_dtype, scales_out):
+        q, h = FUSED_ADD(x, residual, weight, fp8_scale, eps, zero_centered, FP8,
+                         outputs={"out": out, "residual_out": residual_out})
+        return q, fp8_scale.reshape(()), h
+    return FUSED_QUANT(x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype,
+                       outputs={"out": out, "scales_out": scales_out, "residual_out": residual_out})
