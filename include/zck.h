@@ -140,6 +140,21 @@ int zck_gated_gemm_bf16(const void* a, const void* w_gate, const void* w_up, voi
 int zck_gemm_bf16(const void* a, const void* b, void* out, const void* bias, const void* residual,
                   const ZckGemmSizes* sizes, int device, void* stream);
 
+/* Replaces `product_launch("rowwise" | "rowwise_fast", "store", ...)` (src/zig_cu_kernels/fp8_gemm.py:354-383 with
+ * `family_of`, :71-74; epilogue zig/fp8_gemm_sm89.zig:1394-1432): tensorwise and rowwise scales.
+ * out = epilogue(fp32(sum) * fp32(scale_a[i * sa_row] * scale_b[j * sb_row])) with FP32 scales; a stride of 0 makes a
+ * scale tensorwise. k % 16 == 0, n % 8 == 0. The tile is accumulated over all of k in FP32 tensor memory, with and
+ * without the reference's `use_fast_accum`. Of `sizes`: a_stride, b_stride, sa_row, sb_row, su_row, out_stride,
+ * residual_stride, m, n, k, activation are read. */
+int zck_fp8_gemm_rowwise(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out,
+                         const void* bias, const void* residual, const ZckGemmSizes* sizes, int device, void* stream);
+
+/* The gated form (`product_launch(..., "gated", ...)`, fp8_gemm.py:475-508): scale_gate / scale_up per weight row. */
+int zck_fp8_gated_gemm_rowwise(const void* a, const void* w_gate, const void* w_up, const void* scale_a,
+                               const void* scale_gate, const void* scale_up, void* out, const void* bias_gate,
+                               const void* bias_up, const void* residual, const ZckGemmSizes* sizes, int device,
+                               void* stream);
+
 /* No counterpart in the reference (its launchers always get their workspace from the caller's allocator).
  * zck_fp8_gemm for a host that must not allocate device memory: a program that calls this ABI straight from a
  * serving loop, with no caching allocator behind it. Such a host has typically given all free HBM to its own arena at

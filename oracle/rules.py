@@ -174,6 +174,27 @@ def fp8_gated_gemm(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate=Non
     return out.reshape(*lead, w_gate.shape[0])
 
 
+def rowwise_sums(a, scale_a, b, scale_b):
+    """FP32 sums of a tensorwise or rowwise product: `fp32(s) * fp32(scale_a * scale_b)` with the exact sum `s` of the
+    code products. tests/test_fp8_gemm.py:708-716 (`special_expected`, the branch for scalings other than block128)."""
+    m, n = math.prod(a.shape[:-1]), b.shape[0]
+    factor = scale_a.float().reshape(-1, 1).expand(m, 1) * scale_b.float().reshape(1, -1).expand(1, n)
+    return (a.reshape(m, -1).double() @ b.double().T).float() * factor
+
+
+def fp8_gemm_rowwise(a, b, scale_a, scale_b, bias=None, act="none", residual=None):
+    """`fp8_gemm` with tensorwise (one element) or rowwise (`(m, 1)`, `(n, 1)`) FP32 scales.
+    src/zig_cu_kernels/fp8_gemm.py:51-83; tests/test_fp8_gemm.py:497-502 (`store_expected`)."""
+    return store_epilogue(rowwise_sums(a, scale_a, b, scale_b), bias, act, residual)
+
+
+def fp8_gated_gemm_rowwise(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate=None, bias_up=None, act="silu",
+                           residual=None):
+    """The gated form. tests/test_fp8_gemm.py:505-509 (`gated_expected`)."""
+    return gated_epilogue(rowwise_sums(a, scale_a, w_gate, scale_gate), rowwise_sums(a, scale_a, w_up, scale_up),
+                          bias_gate, bias_up, act, residual)
+
+
 def gated_gemm_bf16(a, w_gate, w_up, bias_gate=None, bias_up=None, act="silu", residual=None):
     """BF16 `gated_gemm`: exact (FP64) sums of BF16 products, then the BF16 rounding points.
     tests/test_gemm.py:80-101 (`sums_of`, `biased`, `gated_reference`)."""

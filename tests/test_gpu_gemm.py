@@ -331,8 +331,99 @@ def test_layouts_aliases_and_errors(ops):
         ops.fp8_gemm(a, b, scale_a, scale_b, bias=torch.zeros(n + 8, device="cuda", dtype=BF16))
     with pytest.raises(ValueError, match="must be on cuda"):
         ops.fp8_gemm(a, b.cpu(), scale_a, scale_b)
-    with pytest.raises(NotImplementedError):
-        ops.fp8_gemm(a, b, torch.ones(m, 1, device="cuda"), torch.ones(n, 1, device="cuda"))
+    with pytest.raises(ValueError, match="E8M0 scales need block128"):
+        ops.fp8_gemm(a, b, torch.ones(m, 1, device="cuda").to(E8M0), torch.ones(n, 1, device="cuda").to(E8M0))
+
+
+# ---- tensorwise and rowwise scales (the reference's tests/test_fp8_gemm.py:524-560 exact products, :617-632 products
+# against torch._scaled_mm, :708-716 IEEE rule `bf16(fp32(s) * fp32(scale_a * scale_b))`) -----------------------------
+
+def rowwise_scales(mode, m, n, generator, exact):
+    if mode == "tensorwise":
+        if exact:
+            e = torch.randint(-4, 5, (2,), device="cuda", generator=generator).float()
+            return torch.exp2(e[0]).reshape(()), torch.exp2(e[1]).reshape(1, 1)
+        return (torch.rand((), device="cuda", generator=generator) + 0.5) * 0.02, \
+               (torch.rand(1, 1, device="cuda", generator=generator) + 0.5) * 0.02
+    if exact:
+        return (torch.exp2(torch.randint(-3, 4, (m, 1), device="cuda", generator=generator).float()),
+                torch.exp2(torch.randint(-3, 4, (n, 1), device="cuda", generator=generator).float()))
+    return ((torch.rand(m, 1, device="cuda", generator=generator) + 0.5) * 0.02,
+            (torch.rand(n, 1, device="cuda", generator=generator) + 0.5) * 0.02)
+
+
+@pytest.mark.parametrize("mode", ("tensorwise", "rowwise"))
+@pytest.mark.parametrize("fast", (False, True))
+def test_rowwise_exact_products_are_bitwise(ops, mode, fast):
+    generator = torch.Generator(device="cuda").manual_seed(11)
+    for m, n, k in ((70, 384, 1024), (129, 136, 512), (1, 8, 16), (300, 520, 1040), (16, 4096, 2048)):
+        a = torch.randint(-1, 2, (m, k), device="cuda", generator=generator).float().to(FP8)
+        b = torch.randint(-1, 2, (n, k), device="cuda", generator=generator).float().to(FP8)
+        up = torch.randint(-1, 2, (n, k), device="cuda", generator=generator).float().to(FP8)
+        scale_a, scale_b = rowwise_scales(mode, m, n, generator, True)
+        bias = torch.randn(n, device="cuda", generator=generator).bfloat16()
+        bias_up = torch.randn(n, device="cuda", generator=generator).bfloat16()
+        residual = torch.randn(m, n, device="cuda", generator=generator).bfloat16()
+        for activation in ("none", "silu", "gelu", "gelu_tanh"):
+            out = ops.fp8_gemm(a, b, scale_a, scale_b, bias=bias, activation=activation, residual=residual,
+                               use_fast_accum=fast)
+            expected = rules.fp8_gemm_rowwise(a, b, scale_a, scale_b, bias, activation, residual)
+            assert_same_bits(out.cpu(), expected.cpu(), f"store {mode} {m}x{n}x{k} {activation}")
+            out = ops.fp8_gated_gemm(a, b, up, scale_a, scale_b, scale_b, bias_gate=bias, bias_up=bias_up,
+                                     activation=activation, residual=residual, use_fast_accum=fast)
+            expected = rules.fp8_gated_gemm_rowwise(a, b, up, scale_a, scale_b, scale_b, bias, bias_up, activation, residual)
+            assert_same_bits(out.cpu(), expected.cpu(), f"gated {mode} {m}x{n}x{k} {activation}")
+
+
+@pytest.mark.parametrize("mode", ("tensorwise", "rowwise"))
+def test_rowwise_products_meet_the_bound_and_scaled_mm(ops, mode):
+    """Every element within 1.01 * (2^-9 * sum |A_j B_j| + 2^-8 |exact|) of the FP64 product of the dequantized operands,
+    and the largest error at most twice that of torch._scaled_mm plus 2^-8 of the largest exact value."""
+    generator = torch.Generator(device="cuda").manual_seed(12)
+    for m, n, k in ((256, 512, 4096), (64, 1024, 8192), (333, 264, 1008), (2048, 2048, 2048)):
+        x = torch.randn(m, k, device="cuda", generator=generator)
+        w = torch.randn(n, k, device="cuda", generator=generator) / 8
+        if mode == "tensorwise":
+            scale_a, scale_b = (x.abs().amax() / 448).reshape(()), (w.abs().amax() / 448).reshape(1, 1)
+        else:
+            scale_a, scale_b = x.abs().amax(1, keepdim=True) / 448, w.abs().amax(1, keepdim=True) / 448
+        a, b = (x / scale_a).clamp(-448, 448).to(FP8), (w / scale_b).clamp(-448, 448).to(FP8)
+        A, B = a.double() * scale_a.double(), b.double() * scale_b.double()
+        exact, magnitude = A @ B.T, A.abs() @ B.abs().T
+        allowed = 1.01 * (2.0**-9 * magnitude + 2.0**-8 * exact.abs()) + 2.0**-126
+        for fast in (False, True):
+            out = ops.fp8_gemm(a, b, scale_a, scale_b, use_fast_accum=fast)
+            error = (out.double() - exact).abs()
+            assert bool((error <= allowed).all()), f"{mode} {m}x{n}x{k}: excess {float((error - allowed).max())}"
+            if k % 16 == 0 and n % 16 == 0:
+                pt = torch._scaled_mm(a, b.t(), scale_a.reshape(-1, 1) if mode == "rowwise" else scale_a,
+                                      scale_b.reshape(1, -1) if mode == "rowwise" else scale_b.reshape(()),
+                                      out_dtype=BF16, use_fast_accum=fast)
+                assert float(error.amax()) <= 2 * float((pt.double() - exact).abs().amax()) + 2.0**-8 * float(exact.abs().amax())
+
+
+def test_rowwise_all_ones_sum_is_exact_and_special_values_follow_ieee(ops):
+    m, n, k = 16, 128, 32768
+    a, b = torch.ones(m, k, device="cuda").to(FP8), torch.ones(n, k, device="cuda").to(FP8)
+    one = torch.ones((), device="cuda")
+    out = ops.fp8_gemm(a, b, one, one)
+    assert bool((out == k).all()), "the FP32 accumulation in tensor memory lost ones"
+    generator = torch.Generator(device="cuda").manual_seed(13)
+    m, n, k = 64, 256, 256
+    a = torch.randint(-1, 2, (m, k), device="cuda", generator=generator).float().to(FP8)
+    b = torch.randint(-1, 2, (n, k), device="cuda", generator=generator).float().to(FP8)
+    nan_a = a.clone()
+    nan_a.view(torch.uint8)[3, 17] = 0x7F
+    cases = {"NaN codes": (nan_a, torch.ones((), device="cuda"), torch.ones((), device="cuda")),
+             "overflow": (a, torch.tensor(2.0**100, device="cuda"), torch.tensor(2.0**100, device="cuda")),
+             "underflow": (a, torch.tensor(2.0**-100, device="cuda"), torch.tensor(2.0**-100, device="cuda")),
+             "subnormal": (a, torch.tensor(2.0**-140, device="cuda"), torch.tensor(2.0**4, device="cuda")),
+             "NaN scale": (a, torch.tensor(float("nan"), device="cuda"), torch.ones((), device="cuda")),
+             "infinite scale": (a, torch.tensor(float("inf"), device="cuda"), torch.ones((), device="cuda"))}
+    for name, (codes, scale_a, scale_b) in cases.items():
+        out = ops.fp8_gemm(codes, b, scale_a, scale_b)
+        expected = (rules.rowwise_sums(codes, scale_a, b, scale_b) + 0.0).bfloat16()
+        assert_same_bits(out.cpu(), expected.cpu(), name)
 
 
 def test_no_wait_ran_out(ops):

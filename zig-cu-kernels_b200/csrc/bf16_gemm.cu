@@ -1,9 +1,12 @@
-// BF16 x BF16 GEMM with the gated (SwiGLU / GeGLU / bilinear) and plain epilogues, for sm_100a.
+// GEMMs whose tiles are accumulated over all of K in tensor memory, with the gated (SwiGLU / GeGLU / bilinear) and
+// plain epilogues, for sm_100a: BF16 x BF16, and E4M3 x E4M3 with rowwise or tensorwise scales (one scale per row of
+// each operand, or one per operand), which multiply the finished sum.
 //
-// Same skeleton as the FP8 kernel (persistent CTAs, TMA ring, tcgen05.mma into tensor memory, two epilogue
-// warpgroups), without block scales: the tensor core accumulates a whole tile over K in FP32 (kind::f16, four K=16
-// steps per 64-deep stage) and the epilogue drains a tile once, while the next tile already fills the other
-// tensor-memory buffer. Partial K blocks and partial tiles are zero-filled by the TMA unit.
+// Same skeleton as the block-scaled FP8 kernel (persistent CTAs, TMA ring, tcgen05.mma into tensor memory, two
+// epilogue warpgroups), without block scales: the tensor core accumulates a whole tile over K in FP32 (kind::f16, four
+// K=16 steps per 64-deep stage; kind::f8f6f4, four K=32 steps per 128-deep stage: the same 128 bytes per row) and the
+// epilogue drains a tile once, while the next tile already fills the other tensor-memory buffer. Partial K blocks and
+// partial tiles are zero-filled by the TMA unit.
 #include <cuda.h>
 
 #include "gemm_common.cuh"
@@ -26,7 +29,9 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
-template <bool GATED, int ACT>
+// FP8: E4M3 operands; the sum of row i and column j is multiplied by fp32(scale_a[i * sa_row] * scale_b[j * sb_row])
+// (gated: scale_u for the up columns) before the epilogue; a stride of 0 makes the scale tensorwise.
+template <bool GATED, int ACT, bool FP8 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_u, const GemmParams p) {
@@ -76,7 +81,7 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->empty[stage]), phase ^ 1u, p, kRoleProducer, stage))) break;
                     const uint32_t full = ptx::smem_addr(&sh->full[stage]);
                     const uint32_t base = tiles_addr + stage * kStageBytes;
-                    const int32_t x = (int32_t)(i * kHalfBK);
+                    const int32_t x = (int32_t)(i * (FP8 ? 2 * kHalfBK : kHalfBK));  // 128 bytes of K per stage
                     ptx::mbar_arrive_expect_tx(full, kStageBytes);
                     ptx::tma_load_2d(base, &map_a, x, (int32_t)c.m0, full);
 #pragma unroll
@@ -98,7 +103,7 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         __syncwarp();
       } else if (warp == kMmaWarp) {
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16(kBM, kBN);
+            constexpr uint32_t idesc = FP8 ? ptx::idesc_e4m3(kBM, kBN) : idesc_bf16(kBM, kBN);
             uint32_t it = 0, tile_count = 0;
             bool ok = true;
             for (uint32_t unit = blockIdx.x; ok && unit < p.units; unit += gridDim.x, ++tile_count) {
@@ -113,8 +118,10 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t base = tiles_addr + stage * kStageBytes;
                     const uint64_t desc_a = ptx::smem_desc_sw128(base), desc_b = ptx::smem_desc_sw128(base + kATile);
 #pragma unroll
-                    for (uint32_t k4 = 0; k4 < kHalfBK / 16; ++k4)
-                        mma_bf16(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, i | k4);
+                    for (uint32_t k4 = 0; k4 < kHalfBK / 16; ++k4) {  // four steps of 32 bytes of K either way
+                        if (FP8) ptx::mma_f8(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, i | k4);
+                        else mma_bf16(tmem_d, desc_a + k4 * 2, desc_b + k4 * 2, idesc, i | k4);
+                    }
                     ptx::mma_commit(ptx::smem_addr(&sh->empty[stage]));
                 }
                 if (ok) ptx::mma_commit(ptx::smem_addr(&sh->tmem_full[buf]));
@@ -156,6 +163,24 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
+            if (FP8 && row < p.m) {
+                // sum * fp32(scale_a * scale_b): the factor is rounded first, as the reference's rule has it.
+                const float sa = static_cast<const float*>(p.scale_a)[(uint64_t)row * p.sa_row];
+                constexpr int kColumns = GATED ? 64 : 128;
+#pragma unroll
+                for (int j = 0; j < kColumns; j += 2) {
+                    // Columns past n read the last scale; their sums are never stored.
+                    const uint64_t c0 = min(col0 + j, p.n - 1), c1 = min(col0 + j + 1, p.n - 1);
+                    const float* weight_scales = static_cast<const float*>(p.scale_b);
+                    acc[j / 2].x = __fmul_rn(acc[j / 2].x, __fmul_rn(sa, __ldg(weight_scales + c0 * p.sb_row)));
+                    acc[j / 2].y = __fmul_rn(acc[j / 2].y, __fmul_rn(sa, __ldg(weight_scales + c1 * p.sb_row)));
+                    if (GATED) {
+                        const float* up_scales = static_cast<const float*>(p.scale_u);
+                        acc[32 + j / 2].x = __fmul_rn(acc[32 + j / 2].x, __fmul_rn(sa, __ldg(up_scales + c0 * p.su_row)));
+                        acc[32 + j / 2].y = __fmul_rn(acc[32 + j / 2].y, __fmul_rn(sa, __ldg(up_scales + c1 * p.su_row)));
+                    }
+                }
+            }
             if (row < p.m) write_row_any<GATED, ACT>(p, acc, row, col0);
         }
     }
@@ -168,6 +193,16 @@ bf16_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 typedef void (*Bf16Kernel)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const GemmParams);
+
+template <bool FP8>
+static Bf16Kernel full_k_kernel_for(bool gated, int activation) {
+    switch (activation) {
+        case ZCK_ACT_SILU: return gated ? bf16_gemm_kernel<true, ZCK_ACT_SILU, FP8> : bf16_gemm_kernel<false, ZCK_ACT_SILU, FP8>;
+        case ZCK_ACT_GELU_TANH: return gated ? bf16_gemm_kernel<true, ZCK_ACT_GELU_TANH, FP8> : bf16_gemm_kernel<false, ZCK_ACT_GELU_TANH, FP8>;
+        case ZCK_ACT_GELU: return gated ? bf16_gemm_kernel<true, ZCK_ACT_GELU, FP8> : bf16_gemm_kernel<false, ZCK_ACT_GELU, FP8>;
+        default: return gated ? bf16_gemm_kernel<true, ZCK_ACT_NONE, FP8> : bf16_gemm_kernel<false, ZCK_ACT_NONE, FP8>;
+    }
+}
 
 static Bf16Kernel bf16_kernel_for(bool gated, int activation) {
     switch (activation) {
@@ -182,8 +217,12 @@ int init_bf16_gemm(int device) {
     (void)device;
     for (int gated = 0; gated < 2; ++gated)
         for (int activation = ZCK_ACT_NONE; activation <= ZCK_ACT_GELU; ++activation)
+        {
             ZCK_CUDA(cudaFuncSetAttribute(bf16_kernel_for(gated, activation), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)kSmemBytes));
+            ZCK_CUDA(cudaFuncSetAttribute(full_k_kernel_for<true>(gated, activation),
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        }
     return ZCK_OK;
 }
 
@@ -193,16 +232,25 @@ static uint64_t bf16_wait_limit_ns() {
     return value ? value : 2000000000ull;
 }
 
+// fp8: E4M3 operands with the three scale pointers (scale_u only when gated); otherwise BF16 operands.
 static int launch_bf16(bool gated, const void* a, const void* b, const void* u, void* out, const void* bias,
-                       const void* bias_u, const void* residual, const ZckGemmSizes* s, int device, void* stream) {
+                       const void* bias_u, const void* residual, const ZckGemmSizes* s, int device, void* stream,
+                       bool fp8 = false, const void* scale_a = nullptr, const void* scale_b = nullptr,
+                       const void* scale_u = nullptr) {
     ZCK_REQUIRE(s != nullptr, "sizes is NULL");
-    ZCK_REQUIRE(s->k > 0 && s->k % 8 == 0 && s->n % 8 == 0, "k and n must be multiples of 8, got k = %u and n = %u", s->k, s->n);
+    const uint32_t element = fp8 ? 1 : 2, k_multiple = 16 / element;
+    ZCK_REQUIRE(s->k > 0 && s->k % k_multiple == 0 && s->n % 8 == 0, "k must be a multiple of %u and n of 8, got k = %u and n = %u",
+                k_multiple, s->k, s->n);
+    ZCK_REQUIRE(!fp8 || (scale_a && scale_b && (!gated || scale_u)), "a scale pointer is NULL");
+    ZCK_REQUIRE(!fp8 || (aligned(scale_a, 4) && aligned(scale_b, 4) && aligned(scale_u, 4)), "the scales must be 4-byte aligned");
+    ZCK_REQUIRE(!fp8 || s->e8m0_bits == 0, "rowwise and tensorwise scales are FP32");
     ZCK_REQUIRE(s->activation >= ZCK_ACT_NONE && s->activation <= ZCK_ACT_GELU, "unknown activation %d", s->activation);
     ZCK_REQUIRE(s->k <= 0x7FFFFF00u && s->m <= 0x7FFFFF00u && s->n <= 0x7FFFFF00u, "m, n or k is too large");
     if (s->m == 0 || s->n == 0) return ZCK_OK;
     ZCK_REQUIRE(a && b && out && (!gated || u), "an operand pointer is NULL");
     ZCK_REQUIRE(aligned(a, 16) && aligned(b, 16) && (!gated || aligned(u, 16)), "a and the weights must start at a multiple of 16 bytes");
-    ZCK_REQUIRE((s->m <= 1 || (s->a_stride % 8 == 0 && s->a_stride >= s->k)) && (s->n <= 1 || (s->b_stride % 8 == 0 && s->b_stride >= s->k)),
+    ZCK_REQUIRE((s->m <= 1 || (s->a_stride % k_multiple == 0 && s->a_stride >= s->k)) &&
+                (s->n <= 1 || (s->b_stride % k_multiple == 0 && s->b_stride >= s->k)),
                 "the row strides of a and the weights must be multiples of 16 bytes and at least k");
     ZCK_REQUIRE(aligned(out, 16) && (s->m <= 1 || s->out_stride % 8 == 0), "out needs 16-byte aligned rows");
     ZCK_REQUIRE(!residual || (aligned(residual, 16) && s->residual_stride % 8 == 0), "residual needs 16-byte aligned rows");
@@ -212,6 +260,8 @@ static int launch_bf16(bool gated, const void* a, const void* b, const void* u, 
     DeviceState* state = device_state(device);
     if (!state) return ZCK_ERR_CUDA;
     GemmParams p = {};
+    p.scale_a = scale_a; p.scale_b = scale_b; p.scale_u = scale_u;
+    p.sa_row = s->sa_row; p.sb_row = s->sb_row; p.su_row = s->su_row;
     p.bias = static_cast<const __nv_bfloat16*>(bias);
     p.bias_u = static_cast<const __nv_bfloat16*>(bias_u);
     p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -223,19 +273,21 @@ static int launch_bf16(bool gated, const void* a, const void* b, const void* u, 
     p.m = s->m; p.n = s->n; p.k = s->k; p.activation = s->activation;
     p.m_tiles = (s->m + kBM - 1) / kBM;
     p.n_tiles = (s->n + (gated ? kBN / 2 : kBN) - 1) / (gated ? kBN / 2 : kBN);
-    p.kblocks = (s->k + kHalfBK - 1) / kHalfBK;
+    const uint32_t stage_k = 128 / element;  // elements of K per stage row
+    p.kblocks = (s->k + stage_k - 1) / stage_k;
     p.splits = 1;
     uint64_t units = (uint64_t)p.m_tiles * p.n_tiles;
     ZCK_REQUIRE(units <= 0x7FFFFFFFull, "too many tiles");
     p.units = (uint32_t)units;
     CUtensorMap map_a, map_b, map_u;
     int code;
-    if ((code = tensor_map_rows(a, s->m, s->k, s->a_stride, kBM, 2, device, &map_a)) != ZCK_OK) return code;
-    if ((code = tensor_map_rows(b, s->n, s->k, s->b_stride, kBoxRows, 2, device, &map_b)) != ZCK_OK) return code;
+    if ((code = tensor_map_rows(a, s->m, s->k, s->a_stride, kBM, element, device, &map_a)) != ZCK_OK) return code;
+    if ((code = tensor_map_rows(b, s->n, s->k, s->b_stride, kBoxRows, element, device, &map_b)) != ZCK_OK) return code;
     map_u = map_b;
-    if (gated && (code = tensor_map_rows(u, s->n, s->k, s->b_stride, kBoxRows, 2, device, &map_u)) != ZCK_OK) return code;
+    if (gated && (code = tensor_map_rows(u, s->n, s->k, s->b_stride, kBoxRows, element, device, &map_u)) != ZCK_OK) return code;
     dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
-    bf16_kernel_for(gated, p.activation)<<<grid, threads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_u, p);
+    Bf16Kernel kernel = fp8 ? full_k_kernel_for<true>(gated, p.activation) : bf16_kernel_for(gated, p.activation);
+    kernel<<<grid, threads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, map_u, p);
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }
@@ -253,4 +305,19 @@ extern "C" int zck_gated_gemm_bf16(const void* a, const void* w_gate, const void
 extern "C" int zck_gemm_bf16(const void* a, const void* b, void* out, const void* bias, const void* residual,
                              const ZckGemmSizes* sizes, int device, void* stream) {
     return launch_bf16(false, a, b, nullptr, out, bias, nullptr, residual, sizes, device, stream);
+}
+
+extern "C" int zck_fp8_gemm_rowwise(const void* a, const void* b, const void* scale_a, const void* scale_b, void* out,
+                                    const void* bias, const void* residual, const ZckGemmSizes* sizes, int device,
+                                    void* stream) {
+    return launch_bf16(false, a, b, nullptr, out, bias, nullptr, residual, sizes, device, stream, true, scale_a, scale_b,
+                       nullptr);
+}
+
+extern "C" int zck_fp8_gated_gemm_rowwise(const void* a, const void* w_gate, const void* w_up, const void* scale_a,
+                                          const void* scale_gate, const void* scale_up, void* out, const void* bias_gate,
+                                          const void* bias_up, const void* residual, const ZckGemmSizes* sizes,
+                                          int device, void* stream) {
+    return launch_bf16(true, a, w_gate, w_up, out, bias_gate, bias_up, residual, sizes, device, stream, true, scale_a,
+                       scale_gate, scale_up);
 }

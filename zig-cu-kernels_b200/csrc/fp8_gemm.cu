@@ -178,14 +178,15 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // (l & 1: up) of epilogue warpgroup l >> 1. All-FP32 launches copy asynchronously (cp.async straight into the
         // ring, the slot's barrier counts the copies' completion; one 16-byte copy per lane when the four row scales
         // are contiguous and aligned, as in the layout the quantizer writes); launches with any E8M0 scale load,
-        // decode and store, which exposes the load latency once per K block but keeps one protocol per launch.
+        // decode and store, which exposes the load latency once per K block (1.3 instead of 2.1 PFLOP/s on the down
+        // projection; an L1 prefetch 8 blocks ahead and batching the loads of a run in registers were both measured
+        // and did not help, the second because this warp has 40 registers) but keeps one protocol per launch.
         // The lanes do not vote on a wait that gave up: whoever gives up leaves, the others follow when their own
         // wait ends (the abort flag is set), and nobody needs the others to make progress.
         const bool all_f32 = (p.e8m0_bits & (GATED ? 7u : 3u)) == 0u;
         const bool packed_rows = p.sa_row == 1 && p.sa_blk % 4 == 0 && (reinterpret_cast<uintptr_t>(p.scale_a) & 15u) == 0;
         const uint32_t wg = (lane >> 1) & 1u, up = lane & 1u;
         const bool brings_weight = lane < 4 && (GATED || up == 0);
-        constexpr uint32_t kScaleAhead = 8;
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
@@ -215,18 +216,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (brings_weight) copy_scale_async(&target->weight[wg][up], up ? p.scale_u : p.scale_b, weight_at);
                     if (hand_over) ptx::cp_async_mbar_arrive(full);  // counts every copy this lane has issued so far
                 } else {
-                    // These loads are waited for, one K block after the other; what hides their latency (about
-                    // 1700 clk while the tiles stream) is an L1 prefetch of the same addresses kScaleAhead K blocks
-                    // earlier, inside the tile (its first blocks pay, the ring absorbs that).
-                    if (i + kScaleAhead < c.kb_count) {
-                        const uint32_t row_bytes = (p.e8m0_bits & 1u) ? 1 : 4, weight_bytes = (p.e8m0_bits & (up ? 4u : 2u)) ? 1 : 4;
-                        for (uint32_t r = 0; r < live_rows; r += (p.sa_row == 1 ? 4 : 1))  // contiguous rows share a line
-                            ptx::prefetch_l1(static_cast<const uint8_t*>(p.scale_a) +
-                                             (row_at + r * p.sa_row + kScaleAhead * p.sa_blk) * row_bytes);
-                        if (brings_weight)
-                            ptx::prefetch_l1(static_cast<const uint8_t*>(up ? p.scale_u : p.scale_b) +
-                                             (weight_at + kScaleAhead * (up ? p.su_blk : p.sb_blk)) * weight_bytes);
-                    }
                     for (uint32_t r = 0; r < live_rows; ++r)
                         target->row[4 * lane + r] = load_scale(p.scale_a, row_at + r * p.sa_row, p.e8m0_bits & 1u);
                     if (brings_weight)

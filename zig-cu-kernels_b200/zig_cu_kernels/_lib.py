@@ -52,6 +52,9 @@ SIGNATURES = {
                                     ctypes.c_int, ptr]),
     "zck_fp8_gated_gemm": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr,
                                           ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
+    "zck_fp8_gemm_rowwise": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
+    "zck_fp8_gated_gemm_rowwise": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr,
+                                                  ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
     "zck_gated_gemm_bf16": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
     "zck_gemm_bf16": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes), ctypes.c_int, ptr]),
     "zck_fp8_gemm_static": (ctypes.c_int, [ptr, ptr, ptr, ptr, ptr, ptr, ptr, ctypes.POINTER(GemmSizes), ctypes.c_int,

@@ -2,8 +2,9 @@
 
 Same schemas, output layouts, aliasing rules and errors as the reference's src/zig_cu_kernels/torch/fp8_gemm.py
 (:183-243 GEMM, :246-327 gated GEMM, :364-408 rows, :411-458 tiles); the part below the `run` seam is the C ABI.
-Only block128 scaling (one scale per row and 128 columns of the activation, one per 128 x 128 weight tile) is built;
-tensorwise and rowwise scale shapes are recognised and rejected with NotImplementedError.
+Block128 scaling (one scale per row and 128 columns of the activation, one per 128 x 128 weight tile) is the hot path;
+tensorwise and rowwise FP32 scales (one element, or `(m, 1)` and `(n, 1)`) multiply the finished sum, and for them
+the tile is accumulated over all of k in FP32 tensor memory whether or not `use_fast_accum` is set.
 """
 
 import ctypes
@@ -91,9 +92,20 @@ def check_product(a, weights, scale_a, weight_scales, use_fast_accum):
     if use_fast_accum and kind == "block128":
         raise ValueError("use_fast_accum does not take block128 scales")
     need_below(LIMIT_32, m=math.prod(lead), n=columns, k=k)
-    if kind != "block128":
-        raise NotImplementedError(f"{kind} scaling is not built in this library yet; only block128 is")
     return kind
+
+
+def row_scale(scale, rows):
+    """A tensorwise or rowwise FP32 scale as `(tensor, row stride)`: stride 0 for one element."""
+    if scale.numel() == 1:
+        flat = scale.reshape(1)
+        return (flat if flat.data_ptr() % 4 == 0 else flat.clone()), 0
+    scale, (row, _) = scale_strides(scale, rows, 1, False)
+    return scale, row
+
+
+def product_kind(a, columns, scale_a, weight_scales):
+    return scaling_type(tuple(a.shape[:-1]), columns, a.shape[-1], scale_a, weight_scales)
 
 
 def scale_strides(scale, rows, groups, column_major_copy):
@@ -193,8 +205,25 @@ def gemm_into(a, b, scale_a, scale_b, bias, residual, activation, use_fast_accum
     if m == 0 or n == 0:
         return
     groups, tile_rows = k // GROUP, -(-n // GROUP)
+    kind = product_kind(a, n, scale_a, (scale_b,))
     target = output_target(out, (a, b, scale_a, scale_b, bias), residual)
     (a, a_stride), (b, b_stride) = readable_rows(a), readable_rows(b)
+    if kind != "block128":
+        # Tensorwise and rowwise scales multiply the finished sum; the tile is accumulated over all of k in FP32
+        # tensor memory whether or not `use_fast_accum` is set.
+        (scale_a, sa_row), (scale_b, sb_row) = row_scale(scale_a, m), row_scale(scale_b, n)
+        bias = bias_operand(bias)
+        residual, residual_stride = residual_operand(residual)
+        sizes = _lib.GemmSizes(a_stride=a_stride, b_stride=b_stride, sa_row=sa_row, sa_blk=0, sb_row=sb_row, sb_blk=0,
+                               su_row=0, su_blk=0, out_stride=writable_rows(target), residual_stride=residual_stride,
+                               m=m, n=n, k=k, e8m0_bits=0, activation=_lib.ACTIVATIONS[activation], splits=1)
+        device = a.get_device()
+        _lib.check(_lib.library().zck_fp8_gemm_rowwise(
+            a.data_ptr(), b.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(), target.data_ptr(), address(bias),
+            address(residual), ctypes.byref(sizes), device, raw_stream(device)))
+        if target is not out:
+            out.copy_(target)
+        return
     scale_a, (sa_row, sa_blk) = scale_strides(scale_a, m, groups, True)
     scale_b, (sb_row, sb_blk) = scale_strides(scale_b, tile_rows, groups, False)
     bias = bias_operand(bias)
@@ -268,12 +297,30 @@ def gated_into(a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_u
     if m == 0 or f == 0:
         return
     groups, tile_rows = k // GROUP, -(-f // GROUP)
+    kind = product_kind(a, f, scale_a, (scale_gate, scale_up))
     target = output_target(out, (a, w_gate, w_up, scale_a, scale_gate, scale_up, bias_gate, bias_up), residual)
     a, a_stride = readable_rows(a)
     (gate, gate_stride), (up, up_stride) = readable_rows(w_gate), readable_rows(w_up)
     if gate_stride != up_stride and f > 1:  # the kernel reads both weights with one row stride
         gate, up = gate.contiguous(), up.contiguous()
         gate_stride = k
+    if kind != "block128":
+        (scale_a, sa_row), (scale_gate, sg_row), (scale_up, su_row) = (
+            row_scale(scale_a, m), row_scale(scale_gate, f), row_scale(scale_up, f))
+        bias_gate, bias_up = bias_operand(bias_gate), bias_operand(bias_up)
+        residual, residual_stride = residual_operand(residual)
+        sizes = _lib.GemmSizes(a_stride=a_stride, b_stride=gate_stride, sa_row=sa_row, sa_blk=0, sb_row=sg_row,
+                               sb_blk=0, su_row=su_row, su_blk=0, out_stride=writable_rows(target),
+                               residual_stride=residual_stride, m=m, n=f, k=k, e8m0_bits=0,
+                               activation=_lib.ACTIVATIONS[activation], splits=1)
+        device = a.get_device()
+        _lib.check(_lib.library().zck_fp8_gated_gemm_rowwise(
+            a.data_ptr(), gate.data_ptr(), up.data_ptr(), scale_a.data_ptr(), scale_gate.data_ptr(),
+            scale_up.data_ptr(), target.data_ptr(), address(bias_gate), address(bias_up), address(residual),
+            ctypes.byref(sizes), device, raw_stream(device)))
+        if target is not out:
+            out.copy_(target)
+        return
     scale_a, (sa_row, sa_blk) = scale_strides(scale_a, m, groups, True)
     scale_gate, (sg_row, sg_blk) = scale_strides(scale_gate, tile_rows, groups, False)
     scale_up, (su_row, su_blk) = scale_strides(scale_up, tile_rows, groups, False)
