@@ -69,6 +69,15 @@ int zck_quantize_fp8_tiles(const void* w, int w_kind, uint64_t w_stride, void* c
                            uint64_t scale_stride, int scale_is_e8m0, uint32_t n, uint32_t k, int device,
                            void* stream);
 
+/* Replaces `launcher.launch_tensorwise(...)` (src/zig_cu_kernels/torch/fp8_gemm.py:492-545, kernels
+ * zig/fp8_quantize.zig:125-185): ops `quantize_fp8_tensorwise` and `quantize_fp8_static`.
+ * x: rows x width values (width % 8 == 0), codes contiguous. amax_scratch != NULL: the scale amax / 448 (1 for amax 0)
+ * of all of x is computed (the 4-byte scratch word is cleared on the stream first, then raised to the bits of the
+ * largest magnitude, NaN included) and written to scale[0]; amax_scratch == NULL: scale[0] is read. An empty x writes
+ * the scale 1 in the first case. */
+int zck_quantize_fp8_tensorwise(const void* x, int x_kind, uint64_t x_stride, void* codes, float* scale,
+                                uint32_t* amax_scratch, uint32_t rows, uint32_t width, int device, void* stream);
+
 /* Replaces `rms_norm.Launch.launch` -> kernels `rms_norm_<x>[_add_<x>]_weight_*_to_<out>_c*`
  * (src/zig_cu_kernels/rms_norm.py:392-477, zig/rms_norm.zig:239-322, :474-549).
  * residual == NULL gives the plain norm of x (then residual_out must be NULL). Otherwise h = x + residual rounded

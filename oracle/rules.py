@@ -89,6 +89,15 @@ def quantize_rows(x, scale_dtype=torch.float32):
     return codes, scales
 
 
+def quantize_tensorwise(x, scale=None):
+    """`quantize_fp8_tensorwise`: one FP32 scale for all of `x` (amax / 448, 1 for amax 0, NaN when a value is NaN), or
+    the given one; `(codes, scale)` with a scale of shape `()`. tests/test_fp8_gemm.py:284-306; zig/fp8_quantize.zig:125-185."""
+    if scale is None:
+        amax = torch.nn.functional.pad(x.float().abs().flatten(), (0, 1)).amax()
+        scale = scale_of(amax, torch.float32)
+    return codes_of(x.float(), scale.reshape(())), scale.reshape(())
+
+
 def quantize_tiles(w, scale_dtype=torch.float32):
     """`quantize_fp8_tiles`: one scale per 128 x 128 tile; rows past `n` in the last tile row do not count.
     src/zig_cu_kernels/torch/fp8_gemm.py:411-458; tests/test_fp8_gemm.py:271-285; zig/fp8_quantize.zig:97-103."""

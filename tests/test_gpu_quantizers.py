@@ -138,3 +138,42 @@ def test_empty_inputs_and_errors(ops):
     with pytest.raises(ValueError, match="matrix"):
         ops.quantize_fp8_tiles(torch.empty(2, 4, 128, device="cuda", dtype=BF16))
     assert math.prod(q.shape) == 0
+
+
+# ---- quantize_fp8_tensorwise / quantize_fp8_static (the reference's tests/test_fp8_gemm.py:284-306) -----------------
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float32))
+def test_tensorwise_quantizers_are_bitwise_equal_to_the_rules(ops, dtype):
+    import math
+    generator = torch.Generator(device="cuda").manual_seed(2)
+    full = (torch.randn(37, 200, device="cuda", generator=generator) * 30).to(dtype)
+    big = (torch.randn(4096, 8192, device="cuda", generator=generator) * 3).to(dtype)
+    cases = {"matrix": full[:, :192], "vector": full.flatten()[:1000], "batched": full[:36].reshape(4, 9, 200),
+             "zeros": torch.zeros(64, 128, device="cuda", dtype=dtype), "underflow": full[:4, :64] * 1e-44,
+             "nan": torch.where(full == full.max(), math.nan, full),
+             "infinity": torch.where(full == full.min(), -math.inf, full), "large": big,
+             "empty rows": torch.empty(2, 0, 16, device="cuda", dtype=dtype),
+             "empty matrix": torch.empty(3, 0, device="cuda", dtype=dtype)}
+    given = torch.full((1, 1), 0.0371, device="cuda")
+    for name, x in cases.items():
+        q, scale = ops.quantize_fp8_tensorwise(x)
+        codes, expected = rules.quantize_tensorwise(x.cpu())
+        assert scale.shape == () and scale.dtype == torch.float32 and q.shape == x.shape, name
+        assert_same_bits(scale.cpu(), expected, f"{name}: scale")
+        assert_same_bits(q.cpu(), codes, f"{name}: codes")
+        q, returned = ops.quantize_fp8_tensorwise(x, given)
+        assert returned.shape == () and returned.data_ptr() == given.data_ptr()
+        assert_same_bits(q.cpu(), rules.quantize_tensorwise(x.cpu(), given.cpu())[0], f"{name}: given scale codes")
+    # outputs given by the caller, a strided destination, and the errors
+    x = full[:, :192]
+    wide = torch.empty(37, 400, device="cuda", dtype=FP8)
+    scale_out = torch.empty(1, device="cuda")
+    q, scale = ops.quantize_fp8_tensorwise(x, out=wide[:, :192], scale_out=scale_out)
+    assert q.data_ptr() == wide.data_ptr() and scale.data_ptr() == scale_out.data_ptr()
+    assert_same_bits(q.cpu(), rules.quantize_tensorwise(x.cpu())[0], "strided codes")
+    with pytest.raises(ValueError):
+        ops.quantize_fp8_tensorwise(full[:, :13])
+    with pytest.raises(ValueError):
+        ops.quantize_fp8_tensorwise(x, given, scale_out=scale_out)
+    with pytest.raises(ValueError):
+        ops.quantize_fp8_tensorwise(x, torch.ones(2, device="cuda"))

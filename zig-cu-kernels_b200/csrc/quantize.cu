@@ -211,6 +211,60 @@ quantize_tiles_kernel(const T* __restrict__ w, uint64_t w_stride, uint8_t* __res
     else store_as(std::integral_constant<Quotient, kByDivision>());
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Tensorwise: one scale for the whole input. Two kernels on the stream: the largest magnitude (block maxima raised
+// into one word with an unsigned atomic max: the bits of non-negative floats, infinity and the canonical NaN order
+// like unsigned integers), then the codes. With a given scale only the second one runs.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kTensorThreads = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kTensorThreads)
+tensor_amax_kernel(const T* __restrict__ x, uint64_t x_stride, uint32_t rows, uint32_t octets_per_row, uint32_t* amax) {
+    __shared__ float warp_amax[kTensorThreads / 32];
+    const uint64_t total = (uint64_t)rows * octets_per_row, step = (uint64_t)gridDim.x * kTensorThreads;
+    float result = 0.0f;
+    for (uint64_t i = (uint64_t)blockIdx.x * kTensorThreads + threadIdx.x; i < total; i += step) {
+        Octet<T> o;
+        o.load(x + (i / octets_per_row) * x_stride + (i % octets_per_row) * 8);
+        result = octet_amax(o, result);
+    }
+    result = max_nan_over_lanes<32>(result);
+    if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x / 32] = result;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < kTensorThreads / 32; ++w) result = max_nan(result, warp_amax[w]);
+        atomicMax(amax, __float_as_uint(result));
+    }
+}
+
+__global__ void store_scale_kernel(float* scale, float value) { *scale = value; }
+
+// amax == nullptr: the scale is read from `scale`; otherwise it is computed from *amax and written to `scale`. Then the
+// blocks take the input from its end, which the amax kernel read last and the L2 may still hold.
+template <typename T>
+__global__ void __launch_bounds__(kTensorThreads)
+tensor_quantize_kernel(const T* __restrict__ x, uint64_t x_stride, uint8_t* __restrict__ codes, uint32_t rows,
+                       uint32_t octets_per_row, float* scale, const uint32_t* amax) {
+    const uint32_t block = amax ? gridDim.x - 1 - blockIdx.x : blockIdx.x;
+    const uint64_t i = (uint64_t)block * kTensorThreads + threadIdx.x;
+    float value;
+    if (amax) {
+        value = scale_f32_of(__uint_as_float(*amax));
+        if (i == 0) *scale = value;
+    } else {
+        value = *scale;
+    }
+    if (i >= (uint64_t)rows * octets_per_row) return;
+    Octet<T> o;
+    o.load(x + (i / octets_per_row) * x_stride + (i % octets_per_row) * 8);
+    const GroupDivider divide = GroupDivider::of(value);
+    // The corrected reciprocal needs |x| <= 448 * scale, which only a scale computed from x guarantees.
+    const uint2 packed = amax && divide.fast ? octet_codes<T, kByCorrection>(o, divide) : octet_codes<T, kByDivision>(o, divide);
+    st_global_v2(codes + i * 8, packed);
+}
+
 static int check_quantizer(const void* x, int kind, uint64_t stride, const void* codes, const void* scales,
                            int scale_is_e8m0, uint32_t rows, uint32_t k, const char* name) {
     ZCK_REQUIRE(kind == ZCK_BF16 || kind == ZCK_F32, "%s must be BF16 or FP32", name);
@@ -266,6 +320,53 @@ extern "C" int zck_quantize_fp8_rows(const void* x, int x_kind, uint64_t x_strid
         if (scale_is_e8m0) ZCK_ROWS(float, true); else ZCK_ROWS(float, false);
     }
 #undef ZCK_ROWS
+    ZCK_CUDA(cudaGetLastError());
+    return ZCK_OK;
+}
+
+extern "C" int zck_quantize_fp8_tensorwise(const void* x, int x_kind, uint64_t x_stride, void* codes, float* scale,
+                                           uint32_t* amax_scratch, uint32_t rows, uint32_t width, int device, void* stream) {
+    ZCK_REQUIRE(x_kind == ZCK_BF16 || x_kind == ZCK_F32, "x must be BF16 or FP32");
+    ZCK_REQUIRE(scale != nullptr && aligned(scale, 4), "scale must be a 4-byte aligned FP32 word");
+    ZCK_REQUIRE(!amax_scratch || aligned(amax_scratch, 4), "amax_scratch must be 4-byte aligned");
+    DeviceGuard guard(device);
+    ZCK_CUDA(guard.error);
+    DeviceState* state = device_state(device);
+    if (!state) return ZCK_ERR_CUDA;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint64_t octets = (uint64_t)rows * (width / 8);
+    if (octets == 0) {
+        // An empty input has the amax 0 and therefore the scale 1.
+        if (amax_scratch) {
+            store_scale_kernel<<<1, 1, 0, s>>>(scale, 1.0f);
+            ZCK_CUDA(cudaGetLastError());
+        }
+        return ZCK_OK;
+    }
+    ZCK_REQUIRE(width % 8 == 0, "the row length must be a multiple of 8, got %u", width);
+    ZCK_REQUIRE(x && codes, "x and codes must not be NULL");
+    const uint64_t element = x_kind == ZCK_BF16 ? 2 : 4;
+    ZCK_REQUIRE(aligned(x, 16) && (rows <= 1 || (x_stride * element) % 16 == 0), "x needs 16-byte aligned rows");
+    ZCK_REQUIRE(rows <= 1 || x_stride >= width, "the row stride of x is below the row length");
+    ZCK_REQUIRE(aligned(codes, 8), "codes must start at a multiple of 8 bytes");
+    const uint64_t blocks = (octets + kTensorThreads - 1) / kTensorThreads;
+    ZCK_REQUIRE(blocks <= 0x7FFFFFFFull, "x is too large for one launch");
+    const uint32_t octets_per_row = width / 8;
+    uint8_t* q = static_cast<uint8_t*>(codes);
+    if (amax_scratch) {
+        ZCK_CUDA(cudaMemsetAsync(amax_scratch, 0, sizeof(uint32_t), s));
+        const uint64_t resident = (uint64_t)state->sm_count * 8;
+        dim3 grid((unsigned)(blocks < resident ? blocks : resident));
+        if (x_kind == ZCK_BF16)
+            tensor_amax_kernel<<<grid, kTensorThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), x_stride, rows, octets_per_row, amax_scratch);
+        else
+            tensor_amax_kernel<<<grid, kTensorThreads, 0, s>>>(static_cast<const float*>(x), x_stride, rows, octets_per_row, amax_scratch);
+        ZCK_CUDA(cudaGetLastError());
+    }
+    if (x_kind == ZCK_BF16)
+        tensor_quantize_kernel<<<(unsigned)blocks, kTensorThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(x), x_stride, q, rows, octets_per_row, scale, amax_scratch);
+    else
+        tensor_quantize_kernel<<<(unsigned)blocks, kTensorThreads, 0, s>>>(static_cast<const float*>(x), x_stride, q, rows, octets_per_row, scale, amax_scratch);
     ZCK_CUDA(cudaGetLastError());
     return ZCK_OK;
 }

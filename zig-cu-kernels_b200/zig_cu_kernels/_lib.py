@@ -42,6 +42,7 @@ SIGNATURES = {
                                              ctypes.c_int, ptr]),
     "zck_quantize_fp8_tiles": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, ptr, u64, ctypes.c_int, u32, u32,
                                               ctypes.c_int, ptr]),
+    "zck_quantize_fp8_tensorwise": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, ptr, ptr, u32, u32, ctypes.c_int, ptr]),
     "zck_fused_add_rms_norm": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, u64, ptr, u64, ptr, ctypes.c_int, ptr, ptr,
                                               ctypes.c_int, u64, u32, u32, ctypes.c_float, ctypes.c_int, ptr]),
     "zck_fused_add_rms_norm_quant": (ctypes.c_int, [ptr, ctypes.c_int, u64, ptr, u64, ptr, u64, ptr, ctypes.c_int, ptr, u64,

@@ -33,7 +33,8 @@ from .common import (
 from .ops import Out, Param, define
 
 __all__ = [
-    "quantize_fp8_rows", "quantize_fp8_tiles", "fp8_gemm", "fp8_gated_gemm",
+    "quantize_fp8_rows", "quantize_fp8_tiles", "quantize_fp8_tensorwise", "fp8_gemm", "fp8_gated_gemm",
+    "quantize_fp8_tensorwise_op", "quantize_fp8_tensorwise_out_op", "quantize_fp8_static_op", "quantize_fp8_static_out_op",
     "fp8_gemm_op", "fp8_gemm_out_op", "fp8_gated_gemm_op", "fp8_gated_gemm_out_op",
     "quantize_fp8_rows_op", "quantize_fp8_rows_out_op", "quantize_fp8_tiles_op", "quantize_fp8_tiles_out_op",
 ]
@@ -482,3 +483,96 @@ def quantize_fp8_tiles(w, *, scale_dtype=torch.float32, out=None, scales_out=Non
     """E4M3 codes of the weight `w [n, k]` and one scale per 128 x 128 tile: `(q, scales)` with contiguous
     `scales (ceil(n/128), k/128)`, ready to be the `b`, `scale_b` of `fp8_gemm`."""
     return QUANTIZE_FP8_TILES(w, scale_dtype, outputs={"out": out, "scales_out": scales_out})
+
+
+# --------------------------------------------------------------------------------------------------------------------
+# quantize_fp8_tensorwise, quantize_fp8_static (reference :461-556)
+# --------------------------------------------------------------------------------------------------------------------
+
+def check_tensorwise(x):
+    need_dtype("x", x, INPUT_DTYPES)
+
+
+def check_tensorwise_sizes(x):
+    need_below(QUANTIZER_VALUES, **{"x.numel()": x.numel()})
+    if (x.dim() == 0 or x.shape[-1] % 8) and x.numel() % 8:
+        raise ValueError(f"x needs a last dimension or a number of values that is a multiple of 8, got {tuple(x.shape)}")
+
+
+def tensorwise_source(x):
+    """`x` (or a copy) as a matrix the kernels can read: `(matrix, rows, width, row stride)`."""
+    flat = x.dim() == 0 or x.shape[-1] % 8 != 0
+    matrix = x.reshape(1, -1) if flat and x.is_contiguous() else x
+    if flat and not x.is_contiguous():
+        matrix = x.contiguous().reshape(1, -1)
+    source, stride = readable_rows(matrix)
+    return source, math.prod(matrix.shape[:-1]), matrix.shape[-1], stride
+
+
+def tensorwise_launch(x, q, scale, amax):
+    source, rows, width, stride = tensorwise_source(x) if x.numel() else (x, 0, 0, 0)
+    codes = codes_target(q, (x, scale))
+    device = x.get_device()
+    _lib.check(_lib.library().zck_quantize_fp8_tensorwise(
+        source.data_ptr() if x.numel() else None, KINDS[x.dtype], stride, codes.data_ptr() if x.numel() else None,
+        scale.data_ptr(), None if amax is None else amax.data_ptr(), rows, width, device, raw_stream(device)))
+    if codes is not q:
+        q.copy_(codes)
+
+
+def tensorwise_into(x, q, scale):
+    if tuple(q.shape) != tuple(x.shape):
+        raise ValueError(f"q must have the shape {tuple(x.shape)}")
+    if scale.numel() != 1:
+        raise ValueError(f"scale must hold one element, got the shape {tuple(scale.shape)}")
+    target = scale if scale.data_ptr() % 4 == 0 and writes_in_place(scale, (x,)) else \
+        torch.empty((), dtype=torch.float32, device=scale.device)
+    amax = torch.empty((), dtype=torch.int32, device=x.device)  # cleared on the stream by the library
+    tensorwise_launch(x, q, target, amax)
+    if target is not scale:
+        scale.copy_(target.reshape(scale.shape))
+
+
+QUANTIZE_FP8_TENSORWISE = define(
+    "quantize_fp8_tensorwise", params=[Param("Tensor", "x")],
+    outs=[Out("q", "out", lambda x: x.new_empty(x.shape, dtype=FP8), FP8),
+          Out("scale", "scale_out", lambda x: x.new_empty((), dtype=torch.float32), torch.float32)],
+    check=check_tensorwise, check_sizes=check_tensorwise_sizes, run=tensorwise_into)
+quantize_fp8_tensorwise_op, quantize_fp8_tensorwise_out_op = QUANTIZE_FP8_TENSORWISE.functional, QUANTIZE_FP8_TENSORWISE.out
+
+
+def check_static(x, scale):
+    need_dtype("x", x, INPUT_DTYPES)
+    need_dtype("scale", scale, (torch.float32,))
+
+
+def check_static_sizes(x, scale):
+    check_tensorwise_sizes(x)
+    if scale.numel() != 1:
+        raise ValueError(f"scale must hold one element, got the shape {tuple(scale.shape)}")
+
+
+def static_into(x, scale, q):
+    if tuple(q.shape) != tuple(x.shape):
+        raise ValueError(f"q must have the shape {tuple(x.shape)}")
+    if x.numel() == 0:
+        return
+    tensorwise_launch(x, q, scale if scale.data_ptr() % 4 == 0 else scale.clone(), None)
+
+
+QUANTIZE_FP8_STATIC = define(
+    "quantize_fp8_static", params=[Param("Tensor", "x"), Param("Tensor", "scale")],
+    outs=[Out("q", "out", lambda x, scale: x.new_empty(x.shape, dtype=FP8), FP8)],
+    check=check_static, check_sizes=check_static_sizes, run=static_into)
+quantize_fp8_static_op, quantize_fp8_static_out_op = QUANTIZE_FP8_STATIC.functional, QUANTIZE_FP8_STATIC.out
+
+
+def quantize_fp8_tensorwise(x, scale=None, *, out=None, scale_out=None):
+    """E4M3 codes of `x` with one FP32 scale, computed from `x` or given as `scale`: `(q, scale)`, scale of shape `()`."""
+    if scale is None:
+        return QUANTIZE_FP8_TENSORWISE(x, outputs={"out": out, "scale_out": scale_out})
+    if scale.numel() != 1 or scale.dtype != torch.float32:
+        raise ValueError(f"scale must be one FP32 element, got {scale.dtype} of the shape {tuple(scale.shape)}")
+    if scale_out is not None:
+        raise ValueError("scale_out must be None when the call gets a scale")
+    return QUANTIZE_FP8_STATIC(x, scale, outputs={"out": out}), scale.reshape(())
