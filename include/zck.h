@@ -116,9 +116,10 @@ typedef struct ZckGemmSizes {
     int32_t splits;           /* K splits chosen by zck_gemm_plan (1 = no workspace) */
 } ZckGemmSizes;
 
-/* Plan query, pure host: fills `sizes->splits` and returns the workspace the launch needs: `part_bytes` of FP32
- * partial tiles and `counters` 32-bit tile counters that must be ZERO before the first launch (the kernel leaves
- * them at zero). Replaces `product_launch(...).part_bytes/.counters` (src/zig_cu_kernels/fp8_gemm.py:288-297). */
+/* Plan query, pure host: fills `sizes->splits` and returns the workspace the launch needs: `part_bytes` (FP32
+ * partial tiles of a split-K plan, then room for the FP32 values of E8M0 scales, which the launch widens there first;
+ * a launch with E8M0 scales and no workspace decodes them inside the GEMM, more slowly) and `counters` 32-bit tile
+ * counters that must be ZERO before the first launch (the kernel leaves them at zero). Replaces `product_launch(...).part_bytes/.counters` (src/zig_cu_kernels/fp8_gemm.py:288-297). */
 int zck_gemm_plan(ZckGemmSizes* sizes, int gated, int device, size_t* part_bytes, uint32_t* counters);
 
 /* Replaces `product_launch("block128", "store", ...)` -> kernel `fp8_gemm_block128_store_*`

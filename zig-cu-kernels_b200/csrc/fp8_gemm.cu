@@ -177,10 +177,11 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         // Lane l brings the scales of rows 4l .. 4l+3 of this CTA's tile; lanes 0-3 also bring the weight scale
         // (l & 1: up) of epilogue warpgroup l >> 1. All-FP32 launches copy asynchronously (cp.async straight into the
         // ring, the slot's barrier counts the copies' completion; one 16-byte copy per lane when the four row scales
-        // are contiguous and aligned, as in the layout the quantizer writes); launches with any E8M0 scale load,
-        // decode and store, which exposes the load latency once per K block (1.3 instead of 2.1 PFLOP/s on the down
-        // projection; an L1 prefetch 8 blocks ahead and batching the loads of a run in registers were both measured
-        // and did not help, the second because this warp has 40 registers) but keeps one protocol per launch.
+        // are contiguous and aligned, as in the layout the quantizer writes); launches that still have an E8M0 scale
+        // here (no workspace to widen it in, see widen_e8m0_kernel) load, decode and store, which exposes the load
+        // latency once per K block (1.3 instead of 2.1 PFLOP/s on the down projection; an L1 prefetch 8 blocks ahead and
+        // batching the loads of a run in registers were both measured and did not help, the second because this warp
+        // has 40 registers) but keeps one protocol per launch.
         // The lanes do not vote on a wait that gave up: whoever gives up leaves, the others follow when their own
         // wait ends (the abort flag is set), and nobody needs the others to make progress.
         const bool all_f32 = (p.e8m0_bits & (GATED ? 7u : 3u)) == 0u;
@@ -556,6 +557,46 @@ static int resident_pairs(int device, int sm_count, cudaLaunchConfig_t config, G
     return clusters;
 }
 
+// E8M0 scales of a launch that has a workspace are widened to FP32 by a small kernel in front of the GEMM, into the
+// workspace behind the split-K parts, so that the GEMM's scale warp can use its asynchronous FP32 path (its E8M0 path
+// waits for a load per K block and runs the kernel at 60%). The widened values are the decoded bytes, so the GEMM's
+// bits do not change. Layouts: scale_a as [K block][rows rounded up to 4] (rows contiguous, 16-byte copies), weight
+// scales as [tile row][K block].
+__global__ void widen_e8m0_kernel(const uint8_t* __restrict__ in, uint64_t in_row, uint64_t in_blk, float* __restrict__ out,
+                                  uint64_t out_row, uint64_t out_blk, uint32_t rows, uint32_t blocks, bool rows_fastest) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)rows * blocks) return;
+    const uint32_t row = rows_fastest ? (uint32_t)(i % rows) : (uint32_t)(i / blocks);
+    const uint32_t blk = rows_fastest ? (uint32_t)(i / rows) : (uint32_t)(i % blocks);
+    out[row * out_row + blk * out_blk] = e8m0_to_f32(in[row * in_row + blk * in_blk]);
+}
+
+struct WidenedScales {
+    size_t offset_a = 0, offset_b = 0, offset_u = 0, bytes = 0;  // offsets from the start of the region
+    uint32_t rows4 = 0, tile_rows = 0, kblocks = 0;
+};
+
+static WidenedScales widened_layout(const ZckGemmSizes& s, bool gated) {
+    WidenedScales w;
+    w.kblocks = s.k / kBK;
+    w.rows4 = (s.m + 3u) & ~3u;
+    w.tile_rows = (s.n + kGroup - 1) / kGroup;
+    size_t at = 0;
+    auto take = [&](bool wanted, size_t floats, size_t* offset) {
+        *offset = at;
+        if (wanted) at += (floats * sizeof(float) + 15) & ~(size_t)15;
+    };
+    take(s.e8m0_bits & 1u, (size_t)w.kblocks * w.rows4, &w.offset_a);
+    take(s.e8m0_bits & 2u, (size_t)w.tile_rows * w.kblocks, &w.offset_b);
+    take(gated && (s.e8m0_bits & 4u), (size_t)w.tile_rows * w.kblocks, &w.offset_u);
+    w.bytes = at;
+    return w;
+}
+
+static size_t split_part_bytes(uint64_t tiles, uint32_t splits) {
+    return splits > 1 ? ((size_t)tiles * splits * kTileFloats * sizeof(float) + 15) & ~(size_t)15 : 0;
+}
+
 static int check_sizes(const ZckGemmSizes* s) {
     ZCK_REQUIRE(s != nullptr, "sizes is NULL");
     ZCK_REQUIRE(s->k > 0 && s->k % kBK == 0, "block128 scaling needs a positive k %% 128 == 0, got %u", s->k);
@@ -609,6 +650,33 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
     p.units = (uint32_t)units;
     ZCK_REQUIRE(p.splits == 1 || (ws_parts && ws_counters && aligned(ws_parts, 16) && aligned(ws_counters, 4)),
                 "a split-K launch needs the workspace of zck_gemm_plan");
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    if ((s->e8m0_bits & (gated ? 7u : 3u)) && ws_parts) {
+        ZCK_REQUIRE(aligned(ws_parts, 16), "the workspace must start at a multiple of 16 bytes");
+        const WidenedScales w = widened_layout(*s, gated);
+        unsigned char* region = static_cast<unsigned char*>(ws_parts) + split_part_bytes((uint64_t)p.m_tiles * p.n_tiles, p.splits);
+        auto widen = [&](const void* in, uint64_t in_row, uint64_t in_blk, size_t offset, uint64_t out_row, uint64_t out_blk,
+                         uint32_t rows, bool rows_fastest) {
+            const uint64_t total = (uint64_t)rows * w.kblocks;
+            widen_e8m0_kernel<<<(unsigned)((total + 255) / 256), 256, 0, cs>>>(
+                static_cast<const uint8_t*>(in), in_row, in_blk, reinterpret_cast<float*>(region + offset), out_row, out_blk,
+                rows, w.kblocks, rows_fastest);
+        };
+        if (s->e8m0_bits & 1u) {
+            widen(scale_a, s->sa_row, s->sa_blk, w.offset_a, 1, w.rows4, s->m, true);
+            p.scale_a = region + w.offset_a; p.sa_row = 1; p.sa_blk = w.rows4;
+        }
+        if (s->e8m0_bits & 2u) {
+            widen(scale_b, s->sb_row, s->sb_blk, w.offset_b, w.kblocks, 1, w.tile_rows, false);
+            p.scale_b = region + w.offset_b; p.sb_row = w.kblocks; p.sb_blk = 1;
+        }
+        if (gated && (s->e8m0_bits & 4u)) {
+            widen(scale_u, s->su_row, s->su_blk, w.offset_u, w.kblocks, 1, w.tile_rows, false);
+            p.scale_u = region + w.offset_u; p.su_row = w.kblocks; p.su_blk = 1;
+        }
+        ZCK_CUDA(cudaGetLastError());
+        p.e8m0_bits = 0;
+    }
 
     CUtensorMap map_a, map_b, map_u;
     if ((code = tensor_map_of(a, s->m, s->k, s->a_stride, kBM, device, &map_a)) != ZCK_OK) return code;
@@ -617,7 +685,6 @@ static int launch_gemm(bool gated, const void* a, const void* b, const void* u, 
     if (gated && (code = tensor_map_of(u, s->n, s->k, s->b_stride, kBoxRows, device, &map_u)) != ZCK_OK) return code;
 
     dim3 grid(min(p.units, (uint32_t)state->sm_count)), threads(kThreads);
-    cudaStream_t cs = static_cast<cudaStream_t>(stream);
     if (use_pairs(*s, p.splits)) {
         // Pair tiles are 256 rows tall; the unit count and the tile walk are in pair tiles.
         p.m_tiles = (s->m + 2 * kBM - 1) / (2 * kBM);
@@ -665,10 +732,9 @@ extern "C" int zck_gemm_plan(ZckGemmSizes* sizes, int gated, int device, size_t*
     ZCK_REQUIRE(tiles <= 0x7FFFFFFFull, "too many tiles");
     uint32_t splits = choose_splits((uint32_t)tiles, sizes->k / kBK, state->sm_count);
     sizes->splits = (int32_t)splits;
-    if (splits > 1) {
-        *part_bytes = (size_t)tiles * splits * kTileFloats * sizeof(float);
-        *counters = (uint32_t)tiles;
-    }
+    if (splits > 1) *counters = (uint32_t)tiles;
+    // Behind the partial tiles: room for the FP32 values of E8M0 scales (see widen_e8m0_kernel).
+    *part_bytes = split_part_bytes(tiles, splits) + widened_layout(*sizes, gated != 0).bytes;
     return ZCK_OK;
 }
 
