@@ -239,13 +239,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
             // Only what the K loop itself needs stays live across it (the epilogue's registers are all spoken for:
             // 128 accumulators and 64 products in flight); the tile's coordinates are worked out again after it.
-            uint32_t kb_count;
-            bool warp_live;
-            {
-                const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
-                kb_count = c.kb_count;
-                warp_live = c.m0 + quarter * 32 < p.m;
-            }
+            const uint32_t kb_count = unit_coord<GATED, PAIR>(p, unit, rank).kb_count;
             float2 acc[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
@@ -266,11 +260,13 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     __syncwarp();  // every lane has the run's last scales in registers: the run can go back
                     if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&sh->scale_empty[run]));
                 }
-                if (warp_live) {
+                {
                     // Drain in four chunks of 32 columns through two register buffers: the loads of chunks 2 and 3
                     // are in flight while chunks 0 and 1 are folded in, and the buffer goes back to the tensor core
                     // as soon as the last load has landed, before the last FMAs. (Requesting the next K block's first
-                    // chunks under those last FMAs was measured and lost 10%.)
+                    // chunks under those last FMAs was measured and lost 10%.) Warps whose 32 rows lie past the end of A
+                    // drain like the others (the products of zero-filled rows; nothing of them is stored): one path
+                    // through the loop keeps it in registers.
                     const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + buf * kBN + group * 128u;
                     const float2 f0x2 = make_float2(f0, f0), f1x2 = make_float2(f1, f1);
                     uint32_t even[32], odd[32];
@@ -299,13 +295,6 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         acc[48 + j] = __ffma2_rn(make_float2(__uint_as_float(odd[2 * j]), __uint_as_float(odd[2 * j + 1])), f1x2, acc[48 + j]);
-                } else {
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_rank(ptx::smem_addr(&sh->tmem_empty[buf]), 0));
-                        else ptx::mbar_arrive(ptx::smem_addr(&sh->tmem_empty[buf]));
-                    }
                 }
             }
             if (!ok) break;
