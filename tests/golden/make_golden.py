@@ -226,7 +226,9 @@ def norm_quant_vectors(ref, out):
 
 
 def main():
-    root = pathlib.Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of bobcao3/zig-cu-kernels>")
+    root = pathlib.Path(sys.argv[1])
     sys.path[:0] = [str(root / "src"), str(root / "tests")]
     import fp8_mm_references as references  # noqa: E402  (the reference's own module)
     from zig_cu_kernels import packs  # noqa: E402  (the reference's own module, torch only)
