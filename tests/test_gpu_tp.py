@@ -28,7 +28,8 @@ def test_tensor_parallel_mlp_matches_one_gpu():
     assert done.returncode == 0 and "TP_CHECK_OK" in done.stdout, done.stdout[-2000:] + done.stderr[-4000:]
 
 
-def test_pipelined_end_to_end_step_on_one_gpu():
+@pytest.mark.parametrize("split", (False, True))
+def test_pipelined_end_to_end_step_on_one_gpu(split):
     """The graph-replayed, chunk-pipelined step with pinned host buffers gives the bits of the plain forward pass,
     step after step (each step reuses the device buffers of the one before)."""
     import sys
@@ -42,7 +43,7 @@ def test_pipelined_end_to_end_step_on_one_gpu():
     w_down = (torch.randn(hidden, inter, device="cuda", generator=generator) / 32).bfloat16()
     mlp = TensorParallelMLP(w_gate, w_up, w_down)
     staged = torch.empty(m, hidden, device="cuda", dtype=torch.bfloat16)
-    replay = mlp.graphed(staged, chunks=4)
+    replay = mlp.graphed(staged, chunks=4, split=split)
     host_in = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
     host_out = torch.empty(m, hidden, dtype=torch.bfloat16).pin_memory()
     for step in range(3):

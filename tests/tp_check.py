@@ -58,6 +58,21 @@ def main():
         error = float((host_out.float().to(device) - expected).abs().max() / whole.abs().max())
         worst = max(worst, error)
         assert error <= 1e-2, f"rank {rank} pipelined step: max relative error {error}"
+    # replays back to back: the exchange of one replay runs under the first kernels of the next
+    for _ in range(4):
+        replay(host_in, host_out)
+    replay.finish()
+    torch.cuda.synchronize()
+    error = float((host_out.float().to(device) - expected).abs().max() / whole.abs().max())
+    worst = max(worst, error)
+    assert error <= 1e-2, f"rank {rank} back-to-back replays: max relative error {error}"
+    device_replay = mlp.graphed(tokens)
+    for _ in range(4):
+        result = device_replay()
+    device_replay.finish()
+    torch.cuda.synchronize()
+    error = float((result.float() - torch.cat(whole.chunk(world)[rank:rank + 1])).abs().max() / whole.abs().max())
+    assert error <= 1e-2, f"rank {rank} device replays: max relative error {error}"
     errors = torch.tensor([worst], device=device)
     dist.all_reduce(errors, op=dist.ReduceOp.MAX)
     if rank == 0:

@@ -77,13 +77,21 @@ class TensorParallelMLP:
         self.kernel_events.setdefault(name, []).append((start, end))
         return result
 
-    def partial(self, tokens, out=None):
-        """BF16 partial `(m, H)` of this rank for `tokens (m, H)`: four kernels."""
+    def front(self, tokens, out=None, scales_out=None):
+        """The first three kernels: quantized activations `(q, scale_q)` of this rank's columns of the up projection."""
         a, scale_a = self._run("quantize_tokens", ops.quantize_fp8_rows, tokens, scale_dtype=self.scale_dtype)
         act = self._run("gated_gemm", ops.fp8_gated_gemm, a, self.gate, self.up, scale_a, self.scale_gate,
                         self.scale_up)
-        q, scale_q = self._run("quantize_act", ops.quantize_fp8_rows, act, scale_dtype=self.scale_dtype)
+        return self._run("quantize_act", ops.quantize_fp8_rows, act, scale_dtype=self.scale_dtype, out=out,
+                         scales_out=scales_out)
+
+    def back(self, q, scale_q, out=None):
+        """The down projection of this rank's K range: the BF16 partial `(m, H)`."""
         return self._run("down_gemm", ops.fp8_gemm, q, self.down, scale_q, self.scale_down, out=out)
+
+    def partial(self, tokens, out=None):
+        """BF16 partial `(m, H)` of this rank for `tokens (m, H)`: four kernels."""
+        return self.back(*self.front(tokens), out=out)
 
     def forward(self, tokens, own_rows=None):
         """`(m, H)` BF16 result: the full sum on every rank (all_reduce) or this rank's `m/world` rows
@@ -116,10 +124,15 @@ class TensorParallelMLP:
         compute.wait_stream(self.comm_stream)
         return result
 
-    def graphed(self, tokens, chunks=None):
+    def graphed(self, tokens, chunks=None, split=None):
         """Binds a replayable forward pass to the fixed buffer `tokens`: the four kernels of every token chunk are
-        captured into one CUDA graph per chunk (one host launch instead of four op calls), while the collectives
-        stay ordinary NCCL calls between the replays. Returns `replay(host_in=None, host_out=None) -> result`.
+        captured into CUDA graphs (one host launch instead of four op calls), while the collectives stay ordinary
+        NCCL calls between the replays. Returns `replay(host_in=None, host_out=None) -> result`.
+
+        With more than one rank a chunk has two graphs, the three kernels in front of the down projection and the
+        down projection itself, and only the second waits for the exchanges that still read the partial sums: the
+        exchange of one replay runs under the first three kernels of the next. The result of a replay is therefore
+        complete on the current stream only after `replay.finish()` (or inside the next replay).
 
         Without arguments `replay` is `forward(tokens)`. With pinned host tensors it is an end-to-end step that is
         pipelined chunk by chunk: this rank's rows of chunk c (`host_in`, `m / world` rows ordered chunk after chunk)
@@ -139,17 +152,33 @@ class TensorParallelMLP:
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(current)
+        split = self.world > 1 if split is None else split  # (one rank: only tests ask for the two-graph form)
+        inter = self.gate.shape[0]
         with torch.cuda.stream(side):  # eager warm-up off the default stream, as graph capture requires
             for lo, hi, _, _ in plan:
                 self.partial(tokens[lo:hi], out=partial[lo:hi])
         current.wait_stream(side)
         torch.cuda.synchronize()
-        graphs = []
+        graphs, staged = [], []
         for lo, hi, _, _ in plan:
             graph = torch.cuda.CUDAGraph()
+            if not split:
+                with torch.cuda.graph(graph):
+                    self.partial(tokens[lo:hi], out=partial[lo:hi])
+                graphs.append((graph, None))
+                continue
+            # The quantized activations live in buffers of their own, outside the graphs' private pools, because
+            # the second graph reads what the first one wrote; `staged` keeps them allocated as long as the replay
+            # function lives (the graphs only know their addresses).
+            codes = torch.empty(hi - lo, inter, dtype=torch.float8_e4m3fn, device=device)
+            scales = torch.empty(inter // GROUP, hi - lo, dtype=self.scale_dtype, device=device).t()
+            staged.append((codes, scales))
             with torch.cuda.graph(graph):
-                self.partial(tokens[lo:hi], out=partial[lo:hi])
-            graphs.append(graph)
+                self.front(tokens[lo:hi], out=codes, scales_out=scales)
+            second = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(second):
+                self.back(codes, scales, out=partial[lo:hi])
+            graphs.append((graph, second))
         self.kernel_events = events
 
         copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
@@ -177,7 +206,7 @@ class TensorParallelMLP:
                         uploaded[c].record(copy_in)
                         offset += rows
             offset = 0
-            for c, (graph, (lo, hi, result_lo, result_hi)) in enumerate(zip(graphs, plan)):
+            for c, ((graph, second), (lo, hi, result_lo, result_hi)) in enumerate(zip(graphs, plan)):
                 if host_in is not None:
                     compute.wait_event(uploaded[c])
                     if self.world > 1:
@@ -185,6 +214,10 @@ class TensorParallelMLP:
                 if host_out is not None and not first:
                     compute.wait_event(downloaded[c])  # the previous step's result chunk has left the device
                 graph.replay()
+                if second is not None:
+                    if self.world > 1:
+                        compute.wait_stream(self.comm_stream)  # earlier exchanges still read the partial sums
+                    second.replay()
                 self.launches += 4
                 consumed[c].record(compute)
                 if self.world > 1:
@@ -204,14 +237,15 @@ class TensorParallelMLP:
                         host_out[offset:offset + piece.shape[0]].copy_(piece, non_blocking=True)
                         downloaded[c].record(copy_out)
                     offset += piece.shape[0]
-            if self.world > 1:
-                compute.wait_stream(self.comm_stream)
             return result
 
         def finish():
             compute = torch.cuda.current_stream()
+            if self.world > 1:
+                compute.wait_stream(self.comm_stream)
             compute.wait_stream(copy_in)
             compute.wait_stream(copy_out)
 
         replay.finish = finish
+        replay.buffers = (partial, result, staged, own)  # owned by the replay function
         return replay
