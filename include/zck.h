@@ -89,16 +89,19 @@ int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stride, const v
                            const float* fp8_scale, void* y, int y_kind, uint64_t y_stride, uint32_t rows,
                            uint32_t width, float eps, int device, void* stream);
 
-/* Replaces the `fp8_blockwise` / `fp8_blockwise_e8m0` outputs of the same launcher: ops `rms_norm_fp8_quant` and
- * `fused_add_rms_norm_fp8_quant` with fp8_scaling="block128" (src/zig_cu_kernels/torch/rms_norm.py:432-434,
- * :499-518; kernel zig/rms_norm.zig:551-615). The BF16 result of the norm is not stored: `codes` (rows of `width`
- * E4M3 bytes, row stride `codes_stride`) and `scales[group * scale_stride + row]` (FP32, or E8M0 bytes) hold the same
- * bits as zck_quantize_fp8_rows gives for that BF16 result. width % 128 == 0; the other rules are those of
- * zck_fused_add_rms_norm (codes rows: 8-byte aligned for BF16 x, 4-byte for FP32 x). */
+/* Replaces the `fp8_blockwise` / `fp8_blockwise_e8m0` / `fp8_rowwise` outputs of the same launcher: ops
+ * `rms_norm_fp8_quant` and `fused_add_rms_norm_fp8_quant` with fp8_scaling="block128" or "rowwise"
+ * (src/zig_cu_kernels/torch/rms_norm.py:432-434, :499-518; kernel zig/rms_norm.zig:551-615). The BF16 result of the
+ * norm is not stored: `codes` (rows of `width` E4M3 bytes, row stride `codes_stride`) and the scales hold the bits
+ * of the quantizer rules applied to that BF16 result. scale_mode ZCK_SCALES_BLOCK_F32 / _BLOCK_E8M0: one scale per row
+ * and 128 values at scales[group * scale_stride + row], width % 128 == 0, the bits of zck_quantize_fp8_rows;
+ * ZCK_SCALES_ROW_F32: one FP32 scale per row (amax / 448, 1 for 0) at scales[row * scale_stride]. The other rules
+ * are those of zck_fused_add_rms_norm (codes rows: 8-byte aligned for BF16 x, 4-byte for FP32 x). */
+enum { ZCK_SCALES_BLOCK_F32 = 0, ZCK_SCALES_BLOCK_E8M0 = 1, ZCK_SCALES_ROW_F32 = 2 };
 int zck_fused_add_rms_norm_quant(const void* x, int x_kind, uint64_t x_stride, const void* residual, uint64_t r_stride,
                                  void* residual_out, uint64_t ro_stride, const void* weight, int weight_kind,
                                  void* codes, uint64_t codes_stride, void* scales, uint64_t scale_stride,
-                                 int scale_is_e8m0, uint32_t rows, uint32_t width, float eps, int device, void* stream);
+                                 int scale_mode, uint32_t rows, uint32_t width, float eps, int device, void* stream);
 
 /* The scalars the reference passes to its GEMM kernels (src/zig_cu_kernels/torch/fp8_gemm.py:226-227, :303-304;
  * zig/fp8_gemm_sm89.zig:387-413, :507-538). Strides in elements; a scale stride of 0 broadcasts. */

@@ -305,6 +305,14 @@ def fused_add_rms_norm(x, residual, weight, eps=1e-6, zero_centered=False, out_d
     return rms_norm(h, weight, zero_centered, eps, out_dtype), h
 
 
+def quantize_rowwise(v):
+    """One FP32 scale per row (amax / 448, 1 for 0) and the codes of `v / scale`: the `"rowwise"` branch of the
+    reference test's `quantize` (tests/test_rms_norm.py:176-191). Scales `(rows, 1)`."""
+    rows = v.reshape(-1, v.shape[-1]).float()
+    scales = scale_of(group_amax(rows, -1), torch.float32).reshape(-1, 1)
+    return codes_of(rows, scales).reshape(v.shape), scales
+
+
 def rms_norm_fp8_quant(h, weight, zero_centered=False, eps=1e-6, scale_dtype=torch.float32):
     """`(codes, scales)` of `rms_norm_fp8_quant(..., fp8_scaling="block128")`: the row quantizer's rules applied to the
     BF16 result of the norm. tests/test_rms_norm.py:176-191 (`quantize`), :445-457 (`queue_fp8_checks`: codes and scales

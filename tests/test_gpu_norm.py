@@ -268,8 +268,8 @@ def test_block_quantized_out_variants_and_errors(ops):
     scale = torch.tensor([0.0123], device="cuda")
     qt, st = ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="tensorwise", fp8_scale=scale)
     assert st.data_ptr() == scale.data_ptr() and qt.dtype == FP8
-    with pytest.raises(NotImplementedError):
-        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="rowwise")
+    with pytest.raises(ValueError):
+        ops.rms_norm_fp8_quant(x, w, EPS, fp8_scaling="rowwise", fp8_scale_dtype=E8M0)
     with pytest.raises(ValueError):
         ops.rms_norm_fp8_quant(x[:, :264], w[:264], EPS, fp8_scaling="block128")
     with pytest.raises(ValueError):
@@ -281,3 +281,34 @@ def test_block_quantized_out_variants_and_errors(ops):
     # empty
     q0, s0 = ops.rms_norm_fp8_quant(x[:0], w, EPS, fp8_scaling="block128")
     assert q0.shape == (0, width) and s0.shape == (0, width // 128)
+
+
+@pytest.mark.parametrize("x_dtype,weight_dtype,zero_centered", [(BF16, BF16, False), (BF16, None, False),
+                                                                (BF16, F32, True), (F32, BF16, False)])
+def test_rowwise_quantized_outputs_quantize_the_bf16_result(ops, x_dtype, weight_dtype, zero_centered):
+    torch.manual_seed(6)
+    for width in (8, 64, 136, 256, 1000, 1032, 4104, 8192, 16392, 32768):
+        if width * (2 if x_dtype == BF16 else 4) > 131072:
+            continue
+        for rows in (1, 6, 13, 67):
+            x = (torch.randn(rows, width, device="cuda") * 3).to(x_dtype)
+            other = (torch.randn(rows, width, device="cuda") * 3).to(x_dtype)
+            if rows > 1:
+                x[rows // 2] = 0
+                other[rows // 2] = 0
+            if rows > 6:
+                x[5, 3] = float("nan")
+            weight = None if weight_dtype is None else (torch.randn(width, device="cuda") * 0.5 + 1).to(weight_dtype)
+            v = ops.rms_norm(x, weight, EPS, zero_centered=zero_centered, out_dtype=BF16)
+            q, scales = ops.rms_norm_fp8_quant(x, weight, EPS, fp8_scaling="rowwise", zero_centered=zero_centered)
+            codes, expected = rules.quantize_rowwise(v.cpu())
+            assert scales.shape == (rows, 1) and scales.dtype == F32
+            assert_same_bits(scales.cpu(), expected, f"scales {width}x{rows}")
+            assert_same_bits(q.cpu(), codes, f"codes {width}x{rows}")
+            v, h = ops.fused_add_rms_norm(x, other, weight, EPS, zero_centered=zero_centered, out_dtype=BF16)
+            q, scales, h2 = ops.fused_add_rms_norm_fp8_quant(x, other, weight, EPS, fp8_scaling="rowwise",
+                                                             zero_centered=zero_centered)
+            codes, expected = rules.quantize_rowwise(v.cpu())
+            assert_same_bits(scales.cpu(), expected, f"fused scales {width}x{rows}")
+            assert_same_bits(q.cpu(), codes, f"fused codes {width}x{rows}")
+            assert_same_bits(h2.cpu(), h.cpu(), "residual_out")

@@ -111,7 +111,7 @@ __device__ __forceinline__ void store_y(void* y, int y_kind, uint64_t offset, co
 }
 
 // Internal output kinds next to ZCK_BF16 / ZCK_F32 / ZCK_FP8_E4M3: E4M3 codes with one computed scale per 128 values.
-constexpr int kBlockF32 = 16, kBlockE8M0 = 17;
+constexpr int kBlockF32 = 16, kBlockE8M0 = 17, kRowF32 = 18;  // kRowF32: one computed FP32 scale per row
 
 // Codes and scale of the V values `v` of one chunk whose group of 128 spans LANES consecutive lanes.
 template <int V, int LANES>
@@ -123,7 +123,10 @@ __device__ __forceinline__ void store_block_quantized(const NormArgs& a, uint64_
         v[i] = bf16_round(v[i]);  // what is quantized is the BF16 result
         amax = max_nan(amax, abs_f32(v[i]));
     }
-    amax = max_nan_over_lanes<LANES>(amax);
+    // Only the lanes of the group take part (the other half of the warp may hold chunks past the end of the row).
+    const uint32_t members = LANES == 32 ? 0xFFFFFFFFu : 0xFFFFu << (threadIdx.x & 16u);
+#pragma unroll
+    for (int mask = LANES / 2; mask > 0; mask >>= 1) amax = max_nan(amax, __shfl_xor_sync(members, amax, mask));
     const bool e8m0 = a.y_kind == kBlockE8M0;
     const uint32_t group = chunk / LANES;
     float q[V];
@@ -227,17 +230,13 @@ __global__ void __launch_bounds__(max_block<XT, C>()) rms_norm_kernel(const Norm
     const float fp8_scale = a.y_kind == ZCK_FP8_E4M3 ? __ldg(a.fp8_scale) : 1.0f;
     const bool zero_centered = (a.weight_kind & ZCK_WEIGHT_ZERO_CENTERED) != 0;
     const int weight = a.weight_kind & 3;
-    const bool blocks = a.y_kind >= kBlockF32;
-    if (!live && !blocks) return;  // with block scales every lane of a warp stays for the shuffles
-#pragma unroll
-    for (int c = 0; c < C; ++c) {
-        uint32_t chunk = c * T + t;
-        // Block scales: groups are whole (width % 128 == 0), so the lanes of a group are all in or all out, and a
-        // warp-uniform test keeps the shuffles converged (T >= 32: one row per warp; T == 16: two rows per warp
-        // with the same chunk index).
-        if (chunk >= a.chunks) continue;
-        float y[V];
+    const bool blocks = a.y_kind == kBlockF32 || a.y_kind == kBlockE8M0, rowwise = a.y_kind == kRowF32;
+    if (!live && !blocks && !rowwise) return;  // with computed scales every lane stays for the shuffles and barriers
+    // y of chunk position c (zeros past the end of the row).
+    auto result_of = [&](int c, float (&y)[V]) {
+        const uint32_t chunk = c * T + t;
         Chunk<XT>::unpack(held[c], y);
+        if (chunk >= a.chunks) return;
 #pragma unroll
         for (int i = 0; i < V; ++i) y[i] = __fmul_rn(y[i], scale);
         if (weight != ZCK_WEIGHT_NONE) {
@@ -255,6 +254,52 @@ __global__ void __launch_bounds__(max_block<XT, C>()) rms_norm_kernel(const Norm
                 for (int i = 0; i < V; ++i) y[i] = __fmul_rn(w[i], y[i]);
             }
         }
+    };
+    if (rowwise) {
+        // One scale per row: the absmax of the BF16 result over the row (same reduction tree as the sum of squares,
+        // NaN kept), then the results once more for the codes.
+        float amax = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            float y[V];
+            result_of(c, y);
+#pragma unroll
+            for (int i = 0; i < V; ++i) amax = max_nan(amax, abs_f32(bf16_round(y[i])));
+        }
+        for (uint32_t mask = lanes / 2; mask > 0; mask >>= 1) amax = max_nan(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, mask));
+        if (T > 32) {
+            __syncthreads();  // everybody has read the sums
+            if ((threadIdx.x & 31) == 0) warp_sums[threadIdx.x / 32] = amax;
+            __syncthreads();
+            const uint32_t warps = T / 32, first = (threadIdx.x / T) * warps;
+            amax = warp_sums[first];
+            for (uint32_t w = 1; w < warps; ++w) amax = max_nan(amax, warp_sums[first + w]);
+        }
+        if (!live) return;
+        const float row_scale = scale_f32_of(amax);
+        if (t == 0) static_cast<float*>(a.scales)[row * a.scale_stride] = row_scale;
+        const GroupDivider divide = GroupDivider::of(row_scale);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+            const uint32_t chunk = c * T + t;
+            if (chunk >= a.chunks) continue;
+            float y[V], q[V];
+            result_of(c, y);
+#pragma unroll
+            for (int i = 0; i < V; ++i) q[i] = divide(bf16_round(y[i]));
+            uint8_t* p = static_cast<uint8_t*>(a.y) + row * a.y_stride + (uint64_t)chunk * V;
+            if (V == 8) st_global_v2(p, make_uint2(e4m3x4_of(q[0], q[1], q[2], q[3]), e4m3x4_of(q[V - 4], q[V - 3], q[V - 2], q[V - 1])));
+            else *reinterpret_cast<uint32_t*>(p) = e4m3x4_of(q[0], q[1], q[2], q[3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+        uint32_t chunk = c * T + t;
+        // Block scales: groups are whole (width % 128 == 0), so the lanes of a group are all in or all out.
+        if (chunk >= a.chunks) continue;
+        float y[V];
+        result_of(c, y);
         if (blocks) store_block_quantized<V, 128 / V>(a, row, chunk, y, live);
         else store_y<V>(a.y, a.y_kind, row * a.y_stride + (uint64_t)chunk * V, y, fp8_scale);
     }
@@ -301,16 +346,16 @@ static int norm_entry(const void* x, int x_kind, uint64_t x_stride, const void* 
                       void* y, int y_kind, uint64_t y_stride, void* scales, uint64_t scale_stride, uint32_t rows,
                       uint32_t width, float eps, int device, void* stream) {
     if (rows == 0 || width == 0) return ZCK_OK;
-    const bool blocks = y_kind >= kBlockF32;
+    const bool blocks = y_kind == kBlockF32 || y_kind == kBlockE8M0, computed = blocks || y_kind == kRowF32;
     ZCK_REQUIRE(x_kind == ZCK_BF16 || x_kind == ZCK_F32, "x must be BF16 or FP32");
-    ZCK_REQUIRE(blocks || y_kind == ZCK_BF16 || y_kind == ZCK_F32 || y_kind == ZCK_FP8_E4M3, "y must be BF16, FP32 or E4M3");
+    ZCK_REQUIRE(computed || y_kind == ZCK_BF16 || y_kind == ZCK_F32 || y_kind == ZCK_FP8_E4M3, "y must be BF16, FP32 or E4M3");
     ZCK_REQUIRE(width % 8 == 0, "the row length must be a multiple of 8, got %u", width);
     ZCK_REQUIRE(!blocks || width % kGroup == 0, "block scales need a row length that is a multiple of 128, got %u", width);
     uint32_t x_bytes = x_kind == ZCK_BF16 ? 2 : 4;
     ZCK_REQUIRE((uint64_t)width * x_bytes <= 131072, "rows of %u values are too wide for this kernel", width);
     ZCK_REQUIRE(x && y, "x and y must not be NULL");
-    ZCK_REQUIRE(!blocks || scales, "scales must not be NULL");
-    ZCK_REQUIRE(!blocks || y_kind == kBlockE8M0 || aligned(scales, 4), "FP32 scales must start at a multiple of 4 bytes");
+    ZCK_REQUIRE(!computed || scales, "scales must not be NULL");
+    ZCK_REQUIRE(!computed || y_kind == kBlockE8M0 || aligned(scales, 4), "FP32 scales must start at a multiple of 4 bytes");
     ZCK_REQUIRE((residual == nullptr) == (residual_out == nullptr), "residual and residual_out go together");
     int weight_base = weight_kind & 3;
     ZCK_REQUIRE(weight_base <= ZCK_WEIGHT_F32 && (weight_kind & ~7) == 0, "unknown weight kind %d", weight_kind);
@@ -362,9 +407,10 @@ extern "C" int zck_fused_add_rms_norm(const void* x, int x_kind, uint64_t x_stri
 extern "C" int zck_fused_add_rms_norm_quant(const void* x, int x_kind, uint64_t x_stride, const void* residual,
                                             uint64_t r_stride, void* residual_out, uint64_t ro_stride,
                                             const void* weight, int weight_kind, void* codes, uint64_t codes_stride,
-                                            void* scales, uint64_t scale_stride, int scale_is_e8m0, uint32_t rows,
+                                            void* scales, uint64_t scale_stride, int scale_mode, uint32_t rows,
                                             uint32_t width, float eps, int device, void* stream) {
+    ZCK_REQUIRE(scale_mode >= ZCK_SCALES_BLOCK_F32 && scale_mode <= ZCK_SCALES_ROW_F32, "unknown scale mode %d", scale_mode);
+    const int kind = scale_mode == ZCK_SCALES_BLOCK_E8M0 ? kBlockE8M0 : scale_mode == ZCK_SCALES_ROW_F32 ? kRowF32 : kBlockF32;
     return norm_entry(x, x_kind, x_stride, residual, r_stride, residual_out, ro_stride, weight, weight_kind, nullptr, codes,
-                      scale_is_e8m0 ? kBlockE8M0 : kBlockF32, codes_stride, scales, scale_stride, rows, width, eps, device,
-                      stream);
+                      kind, codes_stride, scales, scale_stride, rows, width, eps, device, stream);
 }

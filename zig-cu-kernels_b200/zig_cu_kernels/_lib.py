@@ -14,6 +14,7 @@ LIBRARY_NAME = "libzck_b200.so"
 
 BF16, F32, FP8_E4M3 = 0, 1, 2
 ACTIVATIONS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu": 3}
+SCALES_BLOCK_F32, SCALES_BLOCK_E8M0, SCALES_ROW_F32 = 0, 1, 2
 WEIGHT_NONE, WEIGHT_BF16, WEIGHT_F32, WEIGHT_ZERO_CENTERED = 0, 1, 2, 4
 
 u32, u64, i32 = ctypes.c_uint32, ctypes.c_uint64, ctypes.c_int32

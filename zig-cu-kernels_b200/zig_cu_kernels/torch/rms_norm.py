@@ -10,7 +10,7 @@ so results do not depend on the batch.
 `rms_norm_fp8_quant` / `fused_add_rms_norm_fp8_quant` (reference :499-518, ops :432-434): the BF16 result is quantized
 in the same pass. `fp8_scaling="tensorwise"` takes the caller's one-element `fp8_scale`; `"block128"` computes one
 scale per row and 128 values and returns `(q, scales[, residual_out])` with the bits of `quantize_fp8_rows(norm)`;
-`"rowwise"` is part of the reference's surface and not built here.
+`"rowwise"` computes one FP32 scale per row, `scales (rows, 1)`.
 """
 
 import math
@@ -91,15 +91,17 @@ def y_alignment(x, out):
     return min(16, values * out.element_size())
 
 
-def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_out, scales_out=None):
-    """Queues one launch. With `scales_out` (block128 scales, `(rows, width/128)`) `out` holds E4M3 codes."""
+def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_out, scales_out=None, rowwise=False):
+    """Queues one launch. With `scales_out` (block128 scales `(rows, width/128)`, or rowwise scales `(rows, 1)`) `out`
+    holds E4M3 codes."""
     if tuple(out.shape) != tuple(x.shape):
         raise ValueError(f"out must have the shape {tuple(x.shape)}, got {tuple(out.shape)}")
     if residual_out is not None and tuple(residual_out.shape) != tuple(x.shape):
         raise ValueError(f"residual_out must have the shape {tuple(x.shape)}, got {tuple(residual_out.shape)}")
     rows, width = math.prod(x.shape[:-1]), x.shape[-1]
-    if scales_out is not None and tuple(scales_out.shape) != (rows, width // GROUP):
-        raise ValueError(f"scales_out must have the shape {(rows, width // GROUP)}, got {tuple(scales_out.shape)}")
+    scales_shape = (rows, 1) if rowwise else (rows, width // GROUP)
+    if scales_out is not None and tuple(scales_out.shape) != scales_shape:
+        raise ValueError(f"scales_out must have the shape {scales_shape}, got {tuple(scales_out.shape)}")
     if rows == 0 or width == 0:
         return
     # Inputs the kernel cannot address in place are copied once.
@@ -138,6 +140,16 @@ def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_o
         _lib.check(_lib.library().zck_fused_add_rms_norm(
             *leading, None if s_in is None else s_in.data_ptr(), y_target.data_ptr(), KINDS[out.dtype], y_stride,
             rows, width, float(eps), device, raw_stream(device)))
+    elif rowwise:
+        direct = (writes_in_place(scales_out, [*others, *row_inputs]) and scales_out.data_ptr() % 4 == 0 and
+                  (rows <= 1 or scales_out.stride(0) >= 1))
+        scales_target = scales_out if direct else torch.empty((rows, 1), dtype=F32, device=x.device)
+        _lib.check(_lib.library().zck_fused_add_rms_norm_quant(
+            *leading, y_target.data_ptr(), y_stride, scales_target.data_ptr(),
+            scales_target.stride(0) if rows > 1 else 1, _lib.SCALES_ROW_F32, rows, width, float(eps), device,
+            raw_stream(device)))
+        if scales_target is not scales_out:
+            scales_out.copy_(scales_target)
     else:
         # Scales in place when they have the quantizer's layout (rows contiguous, one column per group) and overlap
         # nothing that is read; otherwise through a temporary of that layout.
@@ -148,7 +160,8 @@ def run_norm(x, residual, weight, fp8_scale, eps, zero_centered, out, residual_o
         scales_target = scales_out if direct else block_scales_like(x, scales_out.dtype)
         _lib.check(_lib.library().zck_fused_add_rms_norm_quant(
             *leading, y_target.data_ptr(), y_stride, scales_target.data_ptr(),
-            scales_target.stride(1) if groups > 1 else rows, int(scales_out.dtype == E8M0), rows, width, float(eps),
+            scales_target.stride(1) if groups > 1 else rows,
+            _lib.SCALES_BLOCK_E8M0 if scales_out.dtype == E8M0 else _lib.SCALES_BLOCK_F32, rows, width, float(eps),
             device, raw_stream(device)))
         if scales_target is not scales_out:
             scales_out.copy_(scales_target)
@@ -222,18 +235,22 @@ def check_quant(x, residual, weight, zero_centered, fp8_scaling, fp8_scale_dtype
     check_common(x, residual, weight, None, zero_centered, None)
     need_choice("fp8_scaling", fp8_scaling, COMPUTED_SCALINGS)
     need_choice("fp8_scale_dtype", fp8_scale_dtype, (F32, E8M0) if fp8_scaling == "block128" else (F32,))
-    if fp8_scaling != "block128":
-        raise NotImplementedError(f"fp8_scaling={fp8_scaling!r} is not built in this library yet; only block128 is")
 
 
-def check_quant_sizes(x, residual, weight):
+def check_quant_sizes(x, residual, weight, fp8_scaling):
     check_common_sizes(x, residual, weight, None)
-    if x.shape[-1] % GROUP:
+    if fp8_scaling == "block128" and x.shape[-1] % GROUP:
         raise ValueError(f"fp8_scaling='block128' needs a row length that is a multiple of {GROUP}")
 
 
 def codes_like(x):
     return x.new_empty(x.shape, dtype=FP8)
+
+
+def computed_scales_like(x, fp8_scaling, fp8_scale_dtype):
+    if fp8_scaling == "rowwise":
+        return x.new_empty((math.prod(x.shape[:-1]), 1), dtype=F32)
+    return block_scales_like(x, fp8_scale_dtype)
 
 
 PLAIN_QUANT = define(
@@ -242,13 +259,15 @@ PLAIN_QUANT = define(
             Param("str", "fp8_scaling"), Param("ScalarType", "fp8_scale_dtype")],
     outs=[Out("out", "out", lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: codes_like(x), FP8),
           Out("scales_out", "scales_out",
-              lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: block_scales_like(x, fp8_scale_dtype),
+              lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: computed_scales_like(
+                  x, fp8_scaling, fp8_scale_dtype),
               "fp8_scale_dtype")],
     check=lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant(
         x, None, weight, zero_centered, fp8_scaling, fp8_scale_dtype),
-    check_sizes=lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant_sizes(x, None, weight),
+    check_sizes=lambda x, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant_sizes(
+        x, None, weight, fp8_scaling),
     run=lambda x, weight, eps, zero_centered, fp8_scaling, out, scales_out: run_norm(
-        x, None, weight, None, eps, zero_centered, out, None, scales_out))
+        x, None, weight, None, eps, zero_centered, out, None, scales_out, fp8_scaling == "rowwise"))
 rms_norm_fp8_quant_op, rms_norm_fp8_quant_out_op = PLAIN_QUANT.functional, PLAIN_QUANT.out
 
 FUSED_QUANT = define(
@@ -258,16 +277,16 @@ FUSED_QUANT = define(
     outs=[Out("out", "out",
               lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: codes_like(x), FP8),
           Out("scales_out", "scales_out",
-              lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: block_scales_like(
-                  x, fp8_scale_dtype), "fp8_scale_dtype"),
+              lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: computed_scales_like(
+                  x, fp8_scaling, fp8_scale_dtype), "fp8_scale_dtype"),
           Out("residual_out", "residual_out",
               lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: x.new_empty(x.shape), "x")],
     check=lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant(
         x, residual, weight, zero_centered, fp8_scaling, fp8_scale_dtype),
     check_sizes=lambda x, residual, weight, eps, zero_centered, fp8_scaling, fp8_scale_dtype: check_quant_sizes(
-        x, residual, weight),
+        x, residual, weight, fp8_scaling),
     run=lambda x, residual, weight, eps, zero_centered, fp8_scaling, out, scales_out, residual_out: run_norm(
-        x, residual, weight, None, eps, zero_centered, out, residual_out, scales_out))
+        x, residual, weight, None, eps, zero_centered, out, residual_out, scales_out, fp8_scaling == "rowwise"))
 fused_add_rms_norm_fp8_quant_op, fused_add_rms_norm_fp8_quant_out_op = FUSED_QUANT.functional, FUSED_QUANT.out
 
 
