@@ -34,7 +34,7 @@ CPU_SAMPLE_TOKENS = 128
 # DRAM bytes of one gated-GEMM launch on 4096 tokens (one band of the tile walk), dram__bytes_read.sum +
 # dram__bytes_write.sum from the ncu capture summarised in profiles/fp8_gemm_kernel_4096_tokens_dram_traffic.md.
 # A 16384-token launch walks four such bands, each streaming the weights once, so its traffic is four times this.
-GATED_TRAFFIC_PER_4096_TOKENS = 645336576 + 228346880
+GATED_TRAFFIC_PER_4096_TOKENS = 640222976 + 226347008
 
 
 def peaks():
