@@ -90,7 +90,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             bool ok = true;
             for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
                 const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
-                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                for (uint32_t i = 0; i < (SPLIT ? c.kb_count : p.kblocks); ++i, ++it) {
                     const uint32_t stage = it % kStageCount, phase = (it / kStageCount) & 1u;
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->empty[stage]), phase ^ 1u, p, kRoleProducer, stage))) break;
                     const uint32_t full = ptx::smem_addr(&sh->full[stage]);
@@ -140,7 +140,7 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             bool ok = true;
             for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
                 const TileCoord c = unit_coord<GATED, PAIR>(p, unit, rank);
-                for (uint32_t i = 0; i < c.kb_count; ++i, ++it) {
+                for (uint32_t i = 0; i < (SPLIT ? c.kb_count : p.kblocks); ++i, ++it) {
                     const uint32_t stage = it % kStageCount, phase = (it / kStageCount) & 1u;
                     const uint32_t buf = it & 1u, use = (it >> 1) & 1u;
                     if (!(ok = wait_barrier(sh, ptx::smem_addr(&sh->tmem_empty[buf]), use ^ 1u, p, kRoleMma, 16 + buf))) break;
@@ -239,7 +239,8 @@ fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (uint32_t unit = first_unit; ok && unit < p.units; unit += unit_step) {
             // Only what the K loop itself needs stays live across it (the epilogue's registers are all spoken for:
             // 128 accumulators and 64 products in flight); the tile's coordinates are worked out again after it.
-            const uint32_t kb_count = unit_coord<GATED, PAIR>(p, unit, rank).kb_count;
+            // Unsplit launches give every unit all K blocks: a launch constant that needs no register in the loop.
+            const uint32_t kb_count = SPLIT ? unit_coord<GATED, PAIR>(p, unit, rank).kb_count : p.kblocks;
             float2 acc[64];
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.0f, 0.0f);
