@@ -189,9 +189,12 @@ int zck_fp8_gemm_static(const void* a, const void* b, const void* scale_a, const
  * `zck_poll_status` reads that record from host-mapped memory without synchronizing.
  * (The reference traps after 1 s instead: zig/mm_sm100.zig:58-64.) */
 typedef struct ZckStatus {
-    uint32_t code;   /* 0 = nothing recorded; else 1 + role that gave up */
+    uint32_t code;   /* 0 = nothing recorded; else 1 + role that gave up: 0 TMA producer, 1 MMA issuer, 2 epilogue warp,
+                        3 block-scale producer */
     uint32_t block;  /* blockIdx.x of the first reporter */
-    uint32_t stage;  /* pipeline stage or K block it waited on */
+    uint32_t stage;  /* where it waited. Producer and MMA issuer: the pipeline stage (MMA issuer waiting for a product
+                        buffer: 16 + buffer). Epilogue: the count of K blocks it had drained, top bit set when the scales
+                        of that K block were what never came. Scale producer: the run of ring slots it waited for. */
     uint32_t count;  /* how many reports since the last clear */
 } ZckStatus;
 int zck_poll_status(int device, ZckStatus* out, int clear);

@@ -126,7 +126,7 @@ __device__ __forceinline__ bool wait_barriers(Shared* sh, uint32_t bar, uint32_t
             volatile uint32_t* status = p.status;
             if (status[0] == 0u) {
                 status[1] = blockIdx.x;
-                status[2] = first ? (0x10000u | where) : where;  // bit 16: the second barrier is the one that never came
+                status[2] = first ? (0x80000000u | where) : where;  // top bit: the second barrier is the one that never came
                 status[0] = 1u + role;
             }
             status[3] = status[3] + 1u;
