@@ -426,6 +426,44 @@ def test_rowwise_all_ones_sum_is_exact_and_special_values_follow_ieee(ops):
         assert_same_bits(out.cpu(), expected.cpu(), name)
 
 
+def test_ops_replay_from_cuda_graphs(ops):
+    """One eager call per shape, then capture: the replays give the bits of the eager calls (split-K workspace, E8M0
+    scales widened in the workspace, rowwise scales, the quantizers and the norm with computed scales)."""
+    generator = torch.Generator(device="cuda").manual_seed(21)
+    m, n, k = 96, 512, 2048  # few tiles: a split-K plan
+    x = torch.randn(m, k, device="cuda", generator=generator).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=generator) / 16).bfloat16()
+    weight = torch.ones(k, device="cuda", dtype=BF16)
+
+    def step():
+        q, scales, h = ops.fused_add_rms_norm_fp8_quant(x, x, weight, 1e-6, fp8_scaling="block128")
+        b, scale_b = ops.quantize_fp8_tiles(w)
+        a8, sa8 = ops.quantize_fp8_rows(x, scale_dtype=E8M0)
+        b8, sb8 = ops.quantize_fp8_tiles(w, scale_dtype=E8M0)
+        qt, st = ops.quantize_fp8_tensorwise(x)
+        wt, swt = ops.quantize_fp8_tensorwise(w)
+        return (ops.fp8_gemm(q, b, scales, scale_b), ops.fp8_gemm(a8, b8, sa8, sb8),
+                ops.fp8_gemm(qt, wt, st, swt.reshape(1, 1)), ops.fp8_gated_gemm(q, b, b, scales, scale_b, scale_b))
+
+    eager = [t.clone() for t in step()]
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    for _ in range(3):
+        for t in captured:
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        for index, (got, expected) in enumerate(zip(captured, eager)):
+            assert_same_bits(got.cpu(), expected.cpu(), f"output {index} of the replay")
+
+
 def test_no_wait_ran_out(ops):
     """Runs last in this file: no device-side wait of the GEMM gave up during the tests above."""
     from zig_cu_kernels import _lib
