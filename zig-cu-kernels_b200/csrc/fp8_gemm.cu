@@ -508,7 +508,7 @@ static void tile_counts(const ZckGemmSizes& s, bool gated, uint32_t* m_tiles, ui
 }
 
 // K splits: none while the tiles fill at least half of the SMs; otherwise as many as the SMs hold, each at least
-// 4 K blocks deep. A forced count comes from ZCK_FORCE_SPLITS (tests).
+// 4 K blocks deep, if that shortens a unit's chain by at least 12 K blocks. A forced count comes from ZCK_FORCE_SPLITS (tests).
 static uint32_t choose_splits(uint32_t tiles, uint32_t kblocks, int sm_count) {
     static int forced = [] {
         const char* text = getenv("ZCK_FORCE_SPLITS");
@@ -518,7 +518,10 @@ static uint32_t choose_splits(uint32_t tiles, uint32_t kblocks, int sm_count) {
     if (tiles * 2 >= (uint32_t)sm_count) return 1;
     uint32_t by_sms = (uint32_t)sm_count / tiles, by_depth = kblocks / 4;
     uint32_t splits = min(by_sms, by_depth);
-    return splits < 1 ? 1 : splits;
+    if (splits < 2) return 1;
+    // The exchange of a split plan (partial tiles, counter, the last arriver's sum) costs about as much as a dozen
+    // K blocks of one unit's chain (measured at m = 16: 4.5 us against 0.49 us per K block), so a plan must save more.
+    return kblocks - kblocks / splits >= 12 ? splits : 1;
 }
 
 // CTA pairs serve every unsplit product taller than one 128-row tile (ZCK_GEMM_PAIRS=0 turns them off).
