@@ -426,6 +426,35 @@ def test_rowwise_all_ones_sum_is_exact_and_special_values_follow_ieee(ops):
         assert_same_bits(out.cpu(), expected.cpu(), name)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 520, 512), (512, 768, 1024), (2048, 1024, 2048)])
+def test_e8m0_scales_without_a_workspace_are_decoded_in_the_kernel(ops, m, n, k):
+    """A caller of the C ABI that passes no workspace gets the scale warp's load-decode-store path; the ops always
+    pass one (the scales are widened there first). Both give the same bits."""
+    import ctypes
+    from zig_cu_kernels import _lib
+    generator = torch.Generator(device="cuda").manual_seed(31)
+    x = torch.randn(m, k, device="cuda", generator=generator).bfloat16()
+    w = (torch.randn(n, k, device="cuda", generator=generator) / 16).bfloat16()
+    a, scale_a = ops.quantize_fp8_rows(x, scale_dtype=E8M0)
+    b, scale_b = ops.quantize_fp8_tiles(w, scale_dtype=E8M0)
+    _, scale_a32 = ops.quantize_fp8_rows(x)  # a mixed launch: FP32 row scales, E8M0 weight scales
+    for scales, bits in ((scale_a, 3), (scale_a32, 2)):
+        expected = ops.fp8_gemm(a, b, scales, scale_b) if bits == 3 else None
+        out = torch.empty(m, n, device="cuda", dtype=BF16)
+        sizes = _lib.GemmSizes(a_stride=k, b_stride=k, sa_row=scales.stride(0), sa_blk=scales.stride(1), sb_row=scale_b.stride(0),
+                               sb_blk=scale_b.stride(1), su_row=0, su_blk=0, out_stride=n, residual_stride=0, m=m, n=n, k=k,
+                               e8m0_bits=bits, activation=0, splits=1)
+        device = torch.cuda.current_device()
+        _lib.check(_lib.library().zck_fp8_gemm(a.data_ptr(), b.data_ptr(), scales.data_ptr(), scale_b.data_ptr(),
+                                               out.data_ptr(), None, None, None, None, ctypes.byref(sizes), device,
+                                               torch.cuda.current_stream().cuda_stream))
+        if bits == 3:
+            assert_same_bits(out, expected, "all scales E8M0")
+        else:
+            reference = rules.fp8_gemm(a.cpu(), b.cpu(), scales.cpu(), scale_b.cpu(), dtype=torch.float32)
+            assert max_relative_error(out.cpu(), reference) <= 1e-2
+
+
 def test_ops_replay_from_cuda_graphs(ops):
     """One eager call per shape, then capture: the replays give the bits of the eager calls (split-K workspace, E8M0
     scales widened in the workspace, rowwise scales, the quantizers and the norm with computed scales)."""
